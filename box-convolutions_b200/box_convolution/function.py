@@ -1,0 +1,100 @@
+"""``reparametrize`` and the autograd Function of the box convolution, with the reference's call
+signatures (``box_convolution/box_convolution_function.py:5-65``).
+
+Unlike the reference, the Function does not chain integral_image -> forward and does not save the
+integral image or the output for the backward pass: the fused entry points work from the input
+itself (integral images live on chip for planes that fit there) and the term the reference
+takes from the saved output is recomputed, so only the input and the four parameter tensors are
+kept alive between forward and backward.
+"""
+import torch
+
+from . import _cabi
+from ._cabi import check, lib
+from .ext import _require_cuda_f32, _stream, _workspace
+
+
+def reparametrize(x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
+                  inplace=False, inverse=False):
+    """Scales box parameters between pixel units and the stored, roughly [-1, 1] units.
+    ``inverse=True``: stored -> pixels (multiply by the factors); otherwise pixels -> stored.
+    Returns four new tensors unless ``inplace``."""
+    factor_h = reparametrization_h if inverse else 1 / reparametrization_h
+    factor_w = reparametrization_w if inverse else 1 / reparametrization_w
+    with torch.no_grad():
+        if not inplace:
+            return x_min * factor_h, x_max * factor_h, y_min * factor_w, y_max * factor_w
+        x_min *= factor_h
+        x_max *= factor_h
+        y_min *= factor_w
+        y_max *= factor_w
+
+
+class BoxConvolutionFunction(torch.autograd.Function):
+    """apply(input, x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
+    normalize, exact) -> output (N, C*F, h, w).  The parameters are the stored ones."""
+
+    @staticmethod
+    def forward(ctx, input, x_min, x_max, y_min, y_max,
+                reparametrization_h, reparametrization_w, normalize, exact):
+        _require_cuda_f32(input, "input")
+        if input.dim() != 4:
+            raise RuntimeError("BoxConv2d: input must have 4 dimensions")
+        params = (x_min, x_max, y_min, y_max)
+        for p, n in zip(params, ("x_min", "x_max", "y_min", "y_max")):
+            _require_cuda_f32(p, n)
+            if p.device != input.device:
+                raise RuntimeError("BoxConv2d: input and parameters are on different devices")
+        if not all(p.dim() == 2 for p in params):
+            raise RuntimeError("BoxConv2d: all parameters must have 2 dimensions")
+        N, C, h, w = input.shape
+        if not all(p.size(0) == C for p in params):
+            raise RuntimeError("BoxConv2d: all parameters must have as many rows as there are input channels")
+        F = x_min.size(1)
+        if not all(p.size(1) == F for p in params):
+            raise RuntimeError("BoxConv2d: all parameters must have equal number of columns")
+
+        input = input.contiguous()
+        params = [p.detach().contiguous() for p in params]
+        out = torch.empty((N, C * F, h, w), dtype=torch.float32, device=input.device)
+        with torch.cuda.device(input.device):
+            ws = _workspace(lib.bc_boxconv2d_forward_workspace(N, C, F, h, w), input.device)
+            check(lib.bc_boxconv2d_forward(
+                input.data_ptr(), *[p.data_ptr() for p in params],
+                float(reparametrization_h), float(reparametrization_w), out.data_ptr(),
+                N, C, F, h, w, int(bool(normalize)), int(bool(exact)),
+                ws.data_ptr(), ws.numel(), _stream()), "BoxConv2d forward")
+
+        ctx.normalize, ctx.exact = bool(normalize), bool(exact)
+        ctx.reparametrization_h, ctx.reparametrization_w = reparametrization_h, reparametrization_w
+        ctx.save_for_backward(input, *params)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, x_min, x_max, y_min, y_max = ctx.saved_tensors
+        N, C, h, w = input.shape
+        F = x_min.size(1)
+        needs = ctx.needs_input_grad[:5]
+        mask = sum(1 << i for i, b in enumerate(needs) if b)
+        grad_input = grad_params = None
+        if mask:
+            _require_cuda_f32(grad_output, "grad_output")
+            grad_output = grad_output.contiguous()
+            dev = input.device
+            if needs[0]:
+                grad_input = torch.empty_like(input)
+            if any(needs[1:]):
+                grad_params = torch.empty((4, C, F), dtype=torch.float32, device=dev)
+            with torch.cuda.device(dev):
+                ws = _workspace(lib.bc_boxconv2d_backward_workspace(N, C, F, h, w, mask), dev)
+                check(lib.bc_boxconv2d_backward(
+                    input.data_ptr(), x_min.data_ptr(), x_max.data_ptr(), y_min.data_ptr(),
+                    y_max.data_ptr(), grad_output.data_ptr(),
+                    float(ctx.reparametrization_h), float(ctx.reparametrization_w),
+                    N, C, F, h, w, int(ctx.normalize), int(ctx.exact), mask,
+                    grad_input.data_ptr() if grad_input is not None else None,
+                    grad_params.data_ptr() if grad_params is not None else None,
+                    ws.data_ptr(), ws.numel(), _stream()), "BoxConv2d backward")
+        grads = [grad_input] + [grad_params[i] if needs[1 + i] else None for i in range(4)]
+        return tuple(grads) + (None,) * 4

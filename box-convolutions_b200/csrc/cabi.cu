@@ -1,0 +1,208 @@
+// The extern "C" surface declared in include/boxconv_b200.h: argument checks, workspace
+// carving and dispatch to the kernels.  No allocation, no synchronisation.
+#include <stdio.h>
+#include <string.h>
+
+#include "bc_common.cuh"
+
+namespace bc {
+
+static thread_local char g_last_error[256] = "";
+
+int check_launch(const char *what)
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return BC_OK;
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    return BC_ERR_CUDA;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static inline bool sizes_ok(int N, int C, int F, int h, int w)
+{
+    return N >= 0 && C >= 0 && F >= 0 && h >= 0 && w >= 0 && h < (1 << 24) && w < (1 << 24);
+}
+
+static inline bool any_empty(int N, int C, int F, int h, int w)
+{
+    return N == 0 || C == 0 || F == 0 || h == 0 || w == 0;
+}
+
+static inline size_t integral_bytes(int64_t planes, int h, int w)
+{
+    return align_up((size_t)planes * (size_t)(h + 1) * (size_t)(w + 1) * sizeof(float), 256);
+}
+
+}  // namespace bc
+
+using namespace bc;
+
+extern "C" {
+
+int bc_version(void) { return 100; }
+
+const char *bc_status_string(int status)
+{
+    switch (status) {
+        case BC_OK: return "ok";
+        case BC_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case BC_ERR_BAD_SHAPE: return "invalid or too large size";
+        case BC_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case BC_ERR_CUDA: return "CUDA error at kernel launch";
+        case BC_ERR_UNSUPPORTED: return "unsupported combination of arguments";
+        default: return "unknown status";
+    }
+}
+
+const char *bc_last_cuda_error(void) { return g_last_error; }
+
+int bc_integral_image(const float *in, float *out, int64_t planes, int h, int w, bc_stream_t stream)
+{
+    if (planes < 0 || h < 0 || w < 0 || h >= (1 << 24) || w >= (1 << 24)) return BC_ERR_BAD_SHAPE;
+    if (planes == 0) return BC_OK;
+    if (!out || (!in && h > 0 && w > 0)) return BC_ERR_NULL_POINTER;
+    return launch_integral_image(in, out, planes, h, w, stream);
+}
+
+int bc_box_convolution_forward(const float *input_integrated, const float *x_min,
+                               const float *x_max, const float *y_min, const float *y_max,
+                               float *output, int N, int C, int F, int h, int w, int normalize,
+                               int exact, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (any_empty(N, C, F, h, w)) return BC_OK;
+    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
+    const BoxParams bp{x_min, x_max, y_min, y_max, 1.0f, 1.0f};
+    return launch_forward_global(input_integrated, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+}
+
+size_t bc_box_convolution_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
+{
+    if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
+    return integral_bytes((int64_t)N * C * F, h, w) + align_up(backward_partials_bytes(N, C, F, h, w), 256);
+}
+
+int bc_box_convolution_backward(const float *input_integrated, const float *x_min,
+                                const float *x_max, const float *y_min, const float *y_max,
+                                const float *grad_output, const float *output,
+                                float reparametrization_h, float reparametrization_w, int N,
+                                int C, int F, int h, int w, int normalize, int exact,
+                                int need_mask, float *grad_input, float *grad_params,
+                                void *workspace, size_t workspace_bytes, bc_stream_t stream)
+{
+    (void)output;
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    need_mask &= BC_NEED_ALL;
+    if (!need_mask) return BC_OK;
+    const bool need_params = (need_mask & ~BC_NEED_INPUT) != 0;
+    if (any_empty(N, C, F, h, w)) {
+        // nothing to gather; parameter gradients of an empty batch are zero
+        if (need_params && C > 0 && F > 0) {
+            if (!grad_params) return BC_ERR_NULL_POINTER;
+            for (int j = 0; j < 4; ++j)
+                if (need_mask & (BC_NEED_X_MIN << j))
+                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream) != cudaSuccess)
+                        return check_launch("memset");
+        }
+        return BC_OK;
+    }
+    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !grad_output) return BC_ERR_NULL_POINTER;
+    if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
+    if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
+    const size_t ib = integral_bytes((int64_t)N * C * F, h, w);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < bc_box_convolution_backward_workspace(N, C, F, h, w, need_mask))
+        return BC_ERR_WORKSPACE;
+    float *go_integ = static_cast<float *>(workspace);
+    float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
+
+    int st = launch_integral_image(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
+    if (st != BC_OK) return st;
+    const BoxParams bp{x_min, x_max, y_min, y_max, 1.0f, 1.0f};
+    return launch_backward_global(nullptr, input_integrated, go_integ, bp, reparametrization_h,
+                                  reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
+                                  need_mask, grad_input, grad_params, partials, stream);
+}
+
+int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+                       double reparametrization_h, double reparametrization_w,
+                       double max_input_h, double max_input_w, int exact, bc_stream_t stream)
+{
+    if (count < 0) return BC_ERR_BAD_SHAPE;
+    if (count == 0) return BC_OK;
+    if (!x_min || !x_max || !y_min || !y_max) return BC_ERR_NULL_POINTER;
+    if (reparametrization_h == 0.0 || reparametrization_w == 0.0) return BC_ERR_BAD_SHAPE;
+    return launch_clip(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
+                       max_input_h, max_input_w, exact != 0, stream);
+}
+
+size_t bc_boxconv2d_forward_workspace(int N, int C, int F, int h, int w)
+{
+    if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w)) return 0;
+    return integral_bytes((int64_t)N * C, h, w);
+}
+
+int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_max,
+                         const float *y_min, const float *y_max, float reparametrization_h,
+                         float reparametrization_w, float *output, int N, int C, int F, int h,
+                         int w, int normalize, int exact, void *workspace,
+                         size_t workspace_bytes, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (any_empty(N, C, F, h, w)) return BC_OK;
+    if (!input || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
+    const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
+        return BC_ERR_WORKSPACE;
+    float *integ = static_cast<float *>(workspace);
+    int st = launch_integral_image(input, integ, (int64_t)N * C, h, w, stream);
+    if (st != BC_OK) return st;
+    return launch_forward_global(integ, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+}
+
+size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
+{
+    return bc_box_convolution_backward_workspace(N, C, F, h, w, need_mask);
+}
+
+int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x_max,
+                          const float *y_min, const float *y_max, const float *grad_output,
+                          float reparametrization_h, float reparametrization_w, int N, int C,
+                          int F, int h, int w, int normalize, int exact, int need_mask,
+                          float *grad_input, float *grad_params, void *workspace,
+                          size_t workspace_bytes, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    need_mask &= BC_NEED_ALL;
+    if (!need_mask) return BC_OK;
+    const bool need_params = (need_mask & ~BC_NEED_INPUT) != 0;
+    if (any_empty(N, C, F, h, w)) {
+        if (need_params && C > 0 && F > 0) {
+            if (!grad_params) return BC_ERR_NULL_POINTER;
+            for (int j = 0; j < 4; ++j)
+                if (need_mask & (BC_NEED_X_MIN << j))
+                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream) != cudaSuccess)
+                        return check_launch("memset");
+        }
+        return BC_OK;
+    }
+    if (!input || !x_min || !x_max || !y_min || !y_max || !grad_output) return BC_ERR_NULL_POINTER;
+    if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
+    if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
+    const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
+    const size_t ib = integral_bytes((int64_t)N * C * F, h, w);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < bc_boxconv2d_backward_workspace(N, C, F, h, w, need_mask))
+        return BC_ERR_WORKSPACE;
+    float *go_integ = static_cast<float *>(workspace);
+    float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
+    int st = launch_integral_image(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
+    if (st != BC_OK) return st;
+    return launch_backward_global(input, nullptr, go_integ, bp, reparametrization_h,
+                                  reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
+                                  need_mask, grad_input, grad_params, partials, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+// In-place projection of the stored box parameters (src/box_convolution.cpp:729-763,
+// src/box_convolution_cuda_misc.cu:190-236): clamp both ends of every (min, max) pair to
+// [-(max_size+1), max_size-1] pixels and widen pairs that have become narrower than the minimum
+// size around their mean.  Arithmetic in double on the stored (reparametrized) values, like the
+// reference.  One launch handles the x pair and the y pair.
+#include "bc_common.cuh"
+
+namespace bc {
+
+namespace {
+
+__device__ __forceinline__ void clip_pair(float *pmin, float *pmax, double inv_rep, double min_size, double max_size)
+{
+    const double lo = -(max_size + 1) * inv_rep, hi = (max_size - 1) * inv_rep;
+    double a = fmax(lo, fmin(hi, (double)*pmin));
+    double b = fmax(lo, fmin(hi, (double)*pmax));
+    if (a + (min_size - 0.9999) * inv_rep > b) {
+        const float mean = (float)(0.5 * (a + b));   // rounded to fp32, as the reference does
+        a = mean - 0.5 * (min_size - 0.9999) * inv_rep;
+        b = mean + 0.5 * (min_size - 0.9999) * inv_rep;
+    }
+    *pmin = (float)a;
+    *pmax = (float)b;
+}
+
+__global__ void clip_kernel(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+                            double inv_rep_h, double inv_rep_w, double min_size, double max_h, double max_w)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        clip_pair(x_min + i, x_max + i, inv_rep_h, min_size, max_h);
+    } else if (i < 2 * count) {
+        clip_pair(y_min + (i - count), y_max + (i - count), inv_rep_w, min_size, max_w);
+    }
+}
+
+}  // namespace
+
+int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int count, double rep_h,
+                double rep_w, double max_h, double max_w, bool exact, cudaStream_t s)
+{
+    if (count == 0) return BC_OK;
+    // minimum sizes are single-precision constants in the reference (interface.cpp:405-406)
+    const double min_size = (double)(exact ? 1.001f : 2.001f);
+    const int threads = 128;
+    const int blocks = (2 * count + threads - 1) / threads;
+    clip_kernel<<<blocks, threads, 0, s>>>(x_min, x_max, y_min, y_max, count, 1.0 / rep_h, 1.0 / rep_w,
+                                           min_size, max_h, max_w);
+    return check_launch("clip_parameters");
+}
+
+}  // namespace bc

@@ -1,0 +1,146 @@
+// Zero-padded 2-D inclusive prefix sum, one pass over HBM: every input element is read once and
+// every output element written once (the reference does two column scans and two cuBLAS
+// transposes, src/integral_image_cuda.cu:67-118).
+//
+// One CTA walks down one plane in tiles of `tile_rows` rows.
+//   1. row pass   -- each warp takes rows of the tile; a lane loads 4 adjacent values (one
+//                    128-bit load), sums them, the warp scans the lane totals with shuffles and a
+//                    running carry joins the 128-column segments of a long row.  Results go to
+//                    shared memory already in the output's (w+1)-pitch layout, zero column included.
+//   2. column pass-- one thread per column adds the carry left by the tiles above and walks down
+//                    the tile's rows (bank-conflict free: adjacent lanes, adjacent columns).
+//   3. store pass -- the tile's rows are one contiguous range of the output.  Rows of w+1 floats
+//                    are not 16-byte aligned, so the tile is placed in shared memory at the same
+//                    offset modulo 16 bytes as its destination; the range is then written with
+//                    128-bit stores apart from at most 3 scalar elements at either end.
+#include "bc_common.cuh"
+
+namespace bc {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+__device__ __forceinline__ float warp_inclusive_scan(float v, int lane)
+{
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const float u = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += u;
+    }
+    return v;
+}
+
+template <bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int h, int w, int tile_rows)
+{
+    extern __shared__ float4 smem4[];
+    float *tile = reinterpret_cast<float *>(smem4);           // tile_rows*(w+1) + 4 floats
+    const int pw = w + 1;
+    float *carry = tile + ((tile_rows * pw + 4 + 3) & ~3);    // w floats
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t plane = blockIdx.x;
+    const float *src = in + plane * (int64_t)h * w;
+    float *dst = out + plane * (int64_t)(h + 1) * pw;
+
+    for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
+    for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
+
+    for (int r0 = 0; r0 < h; r0 += tile_rows) {
+        const int rows = min(tile_rows, h - r0);
+        float *gdst = dst + (int64_t)(r0 + 1) * pw;           // where this tile's rows go
+        const int mis = (int)((reinterpret_cast<uintptr_t>(gdst) >> 2) & 3);
+        float *t = tile + mis;
+
+        // ---- 1. row pass
+        for (int i = warp; i < rows; i += kWarps) {
+            const float *row = src + (int64_t)(r0 + i) * w;
+            float *trow = t + i * pw;
+            if (lane == 0) trow[0] = 0.0f;
+            float running = 0.0f;
+            if (VEC4) {
+                const float4 *row4 = reinterpret_cast<const float4 *>(row);
+                const int n4 = w >> 2;
+                float4 nxt = lane < n4 ? __ldg(row4 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int c4 = 0; c4 < n4; c4 += 32) {
+                    float4 v = nxt;
+                    const int j = c4 + 32 + lane;
+                    if (c4 + 32 < n4) nxt = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v.y += v.x; v.z += v.y; v.w += v.z;
+                    const float incl = warp_inclusive_scan(v.w, lane);
+                    const float add = running + (incl - v.w);
+                    running += __shfl_sync(0xffffffffu, incl, 31);
+                    const int c = (c4 + lane) << 2;
+                    if (c < w) {
+                        trow[c + 1] = v.x + add; trow[c + 2] = v.y + add;
+                        trow[c + 3] = v.z + add; trow[c + 4] = v.w + add;
+                    }
+                }
+            } else {
+                for (int c0 = 0; c0 < w; c0 += 32) {
+                    const int c = c0 + lane;
+                    const float v = c < w ? __ldg(row + c) : 0.0f;
+                    const float incl = warp_inclusive_scan(v, lane);
+                    if (c < w) trow[c + 1] = incl + running;
+                    running += __shfl_sync(0xffffffffu, incl, 31);
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- 2. column pass
+        for (int c = tid; c < w; c += kThreads) {
+            float run = carry[c];
+            float *col = t + c + 1;
+            for (int i = 0; i < rows; ++i) {
+                run += col[i * pw];
+                col[i * pw] = run;
+            }
+            carry[c] = run;
+        }
+        __syncthreads();
+
+        // ---- 3. store pass: elements [mis, mis+n) of `tile` go to gdst[-mis ...]
+        const int n = rows * pw;
+        const int end = mis + n;
+        float *gal = gdst - mis;                               // 16-byte aligned
+        for (int s = tid * 4; s < end; s += kThreads * 4) {
+            if (s >= mis && s + 4 <= end) {
+                *reinterpret_cast<float4 *>(gal + s) = *reinterpret_cast<const float4 *>(tile + s);
+            } else {
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    if (s + m >= mis && s + m < end) gal[s + m] = tile[s + m];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+int launch_integral_image(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
+{
+    if (planes == 0) return BC_OK;
+    if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
+    const int pw = w + 1;
+    // rows per tile: about 36 KB of shared memory, never more than the plane has
+    int tile_rows = 9000 / pw;
+    if (tile_rows < 1) tile_rows = 1;
+    if (tile_rows > h) tile_rows = h;
+    const size_t smem = ((size_t)((tile_rows * pw + 4 + 3) & ~3) + (size_t)w) * sizeof(float);
+    if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
+    const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    auto kern = vec4 ? integral_image_kernel<true> : integral_image_kernel<false>;
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return check_launch("integral_image: shared memory opt-in");
+    }
+    kern<<<(unsigned)planes, kThreads, smem, s>>>(in, out, h, w, tile_rows);
+    return check_launch("integral_image");
+}
+
+}  // namespace bc

@@ -1,0 +1,126 @@
+/*
+ * boxconv_b200 -- C ABI of the Blackwell (sm_100a) box-convolution hot path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its kernels on the CUDA
+ * stream it is given and returns without synchronising.  The library never allocates, frees
+ * or copies behind the caller's back: outputs and scratch memory are supplied by the caller
+ * (query the scratch size first).  Return value: BC_OK (0) or a negative BC_ERR_* code;
+ * bc_status_string() gives a short text for it.  There is no CPU implementation behind any of
+ * these calls.
+ *
+ * Conventions (those of the reference project): fp32 everywhere; the "x" axis is rows/height,
+ * "y" is columns/width; box parameters come as four arrays of C*F floats (x_min, x_max, y_min,
+ * y_max) indexed k = c*F + f, in actual pixels unless stated; an integral image of an h x w
+ * plane has (h+1) x (w+1) entries with a zero first row and column.  Tensors are dense and
+ * row-major: input (N,C,h,w), output / grad_output (N,C,F,h,w) == (N,C*F,h,w).
+ *
+ * Each declaration names the reference interface it stands in for (path in the reference
+ * project : lines).
+ */
+#ifndef BOXCONV_B200_H
+#define BOXCONV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same type as cudaStream_t; spelled out so that the header needs no CUDA include. */
+typedef struct CUstream_st *bc_stream_t;
+
+enum {
+    BC_OK = 0,
+    BC_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
+    BC_ERR_BAD_SHAPE = -2,      /* a size is negative, zero where it may not be, or too large */
+    BC_ERR_WORKSPACE = -3,      /* scratch memory missing or too small */
+    BC_ERR_CUDA = -4,           /* the CUDA runtime reported an error at launch */
+    BC_ERR_UNSUPPORTED = -5     /* the combination of arguments is not implemented */
+};
+
+/* need_mask bits of the backward entry points */
+enum {
+    BC_NEED_INPUT = 1,
+    BC_NEED_X_MIN = 2,
+    BC_NEED_X_MAX = 4,
+    BC_NEED_Y_MIN = 8,
+    BC_NEED_Y_MAX = 16,
+    BC_NEED_ALL = 31
+};
+
+int bc_version(void);
+const char *bc_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char *bc_last_cuda_error(void);
+
+/* Zero-padded inclusive 2-D prefix sum of `planes` planes of h x w: in (planes,h,w) ->
+ * out (planes,h+1,w+1).  Replaces integral_image(): src/integral_image_interface.cpp:8-27,
+ * src/integral_image_cuda.cu:67-118 (two column scans and two cuBLAS transposes there; one
+ * pass here). */
+int bc_integral_image(const float *in, float *out, int64_t planes, int h, int w, bc_stream_t stream);
+
+/* Box gather from a ready integral image: input_integrated (N,C,h+1,w+1) -> output
+ * (N,C,F,h,w).  Replaces box_convolution_forward(): src/box_convolution_interface.cpp:13-139
+ * with src/box_convolution_cuda_forward.cu:207-251 and the split/area helpers
+ * src/box_convolution_cuda_misc.cu:16-72,238-301. */
+int bc_box_convolution_forward(const float *input_integrated, const float *x_min,
+                               const float *x_max, const float *y_min, const float *y_max,
+                               float *output, int N, int C, int F, int h, int w, int normalize,
+                               int exact, bc_stream_t stream);
+
+/* Scratch bytes bc_box_convolution_backward() needs for these sizes. */
+size_t bc_box_convolution_backward_workspace(int N, int C, int F, int h, int w, int need_mask);
+
+/* Gradients w.r.t. the input and the four box parameters.  Replaces
+ * box_convolution_backward(): src/box_convolution_interface.cpp:141-395 with
+ * src/box_convolution_cuda_backward.cu:173-190,420-473 and the ATen reductions at
+ * interface.cpp:274,343-391.
+ *   input_integrated (N,C,h+1,w+1); grad_output (N,C,F,h,w);
+ *   output: the forward result.  Accepted for signature compatibility and never read (the
+ *           term the reference takes from it is recomputed); may be NULL.
+ *   grad_input  (N,C,h,w), written iff need_mask & BC_NEED_INPUT;
+ *   grad_params (4,C,F) in the order x_min, x_max, y_min, y_max (src/box_convolution.h:3),
+ *               in reparametrized units (already multiplied by reparametrization_h / _w);
+ *               rows whose need bit is clear are left untouched.
+ * The workspace must be 256-byte aligned. */
+int bc_box_convolution_backward(const float *input_integrated, const float *x_min,
+                                const float *x_max, const float *y_min, const float *y_max,
+                                const float *grad_output, const float *output,
+                                float reparametrization_h, float reparametrization_w, int N,
+                                int C, int F, int h, int w, int normalize, int exact,
+                                int need_mask, float *grad_input, float *grad_params,
+                                void *workspace, size_t workspace_bytes, bc_stream_t stream);
+
+/* In-place projection of the stored (reparametrized) parameters, `count` = C*F values per
+ * array.  Replaces clip_parameters(): src/box_convolution_interface.cpp:397-415 with
+ * src/box_convolution_cuda_misc.cu:190-236 (two launches there, one here). */
+int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+                       double reparametrization_h, double reparametrization_w,
+                       double max_input_h, double max_input_w, int exact, bc_stream_t stream);
+
+/* ---- the module step, fused ------------------------------------------------------------
+ * What BoxConvolutionFunction.forward / .backward do as a chain of extension calls
+ * (box_convolution/box_convolution_function.py:32-65), taken from the input itself: the
+ * parameters are the STORED ones and are multiplied by reparametrization_h / _w in fp32 as
+ * reparametrize() does (function.py:17-27); integral images live in shared memory when a
+ * plane fits there and in the workspace otherwise. */
+size_t bc_boxconv2d_forward_workspace(int N, int C, int F, int h, int w);
+int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_max,
+                         const float *y_min, const float *y_max, float reparametrization_h,
+                         float reparametrization_w, float *output, int N, int C, int F, int h,
+                         int w, int normalize, int exact, void *workspace,
+                         size_t workspace_bytes, bc_stream_t stream);
+
+size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask);
+int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x_max,
+                          const float *y_min, const float *y_max, const float *grad_output,
+                          float reparametrization_h, float reparametrization_w, int N, int C,
+                          int F, int h, int w, int normalize, int exact, int need_mask,
+                          float *grad_input, float *grad_params, void *workspace,
+                          size_t workspace_bytes, bc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOXCONV_B200_H */

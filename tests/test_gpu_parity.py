@@ -1,0 +1,289 @@
+"""Parity of the CUDA library with the oracle and with the golden fixtures produced by the
+reference's own CPU code.  Every call goes through the C ABI (`libboxconv_b200.so`).
+
+Tolerances (max|ours-ref| / max|ref| per tensor): outputs and grad-input 1e-4, parameter
+gradients 1e-3, integral image 1e-5 element-wise relative -- the bars of the task; the asserts
+below use tighter values where the arithmetic allows.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import max_rel
+from oracle import oracle
+from workloads import CONFIGS, make_workload
+
+pytestmark = pytest.mark.gpu
+
+TOL_OUT, TOL_GIN, TOL_PARAM, TOL_II = 1e-4, 1e-4, 1e-3, 1e-5
+
+
+@pytest.fixture(scope="module")
+def bc():
+    import box_convolution
+    assert torch.cuda.is_available()
+    return box_convolution
+
+
+def cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# ------------------------------------------------------------------ integral image
+def test_integral_image_golden(bc, golden):
+    for i in range(int(golden["ii_count"])):
+        got = bc.integral_image(cuda(golden["ii%d_in" % i])).cpu().numpy()
+        ref = golden["ii%d_out" % i]
+        assert got.shape == ref.shape
+        np.testing.assert_allclose(got, ref, rtol=TOL_II, atol=1e-8, err_msg=str(i))
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (2, 3, 10, 10), (3, 7, 13), (5, 64, 64), (2, 2, 64, 128),
+                                   (3, 129, 257), (2, 300, 1000), (1, 40, 2051), (4, 512, 1024), (9, 3)])
+def test_integral_image_random(bc, shape):
+    rng = np.random.default_rng(sum(shape))
+    x = rng.random(shape, dtype=np.float32)
+    got = bc.integral_image(cuda(x)).cpu().numpy()
+    ref = oracle.integral_image(x)
+    np.testing.assert_allclose(got, ref, rtol=TOL_II, atol=1e-8)
+    assert (got[..., 0, :] == 0).all() and (got[..., :, 0] == 0).all()
+
+
+def test_integral_image_noncontiguous_and_unaligned(bc):
+    rng = np.random.default_rng(3)
+    x = rng.random((4, 6, 20, 36), dtype=np.float32)
+    xt = cuda(x)
+    got = bc.integral_image(xt[:, ::2, 1:, 2:]).cpu().numpy()          # strided view, made contiguous
+    np.testing.assert_allclose(got, oracle.integral_image(x[:, ::2, 1:, 2:]), rtol=TOL_II)
+    flat = torch.empty(6 * 20 * 36 + 3, device="cuda")
+    view = flat[3:].view(6, 20, 36)                                     # 4-byte aligned only
+    view.copy_(xt[0])
+    np.testing.assert_allclose(bc.integral_image(view).cpu().numpy(), oracle.integral_image(x[0]), rtol=TOL_II)
+
+
+def test_integral_image_empty(bc):
+    out = bc.integral_image(torch.empty(0, 3, 5, 7, device="cuda"))
+    assert out.shape == (0, 3, 6, 8)
+    out = bc.integral_image(torch.empty(2, 0, 7, device="cuda"))
+    assert out.shape == (2, 1, 8) and (out == 0).all()
+
+
+# ------------------------------------------------------------------ the four-function interface
+def test_four_function_interface_golden(bc, golden):
+    for i in range(int(golden["bc_count"])):
+        pre = "bc%d_" % i
+        N, C, F, h, w, normalize, exact, _ = [int(v) for v in golden[pre + "meta"]]
+        rep_h, rep_w = [float(v) for v in golden[pre + "rep"]]
+        params = [cuda(p) for p in golden[pre + "params"]]
+        integ = bc.integral_image(cuda(golden[pre + "x"]))
+        out = bc.box_convolution_forward(integ, *params, bool(normalize), bool(exact))
+        assert max_rel(out.cpu().numpy(), golden[pre + "out"]) < 1e-5, i
+        res = bc.box_convolution_backward(integ, *params, cuda(golden[pre + "go"]), out, rep_h, rep_w,
+                                          bool(normalize), bool(exact), True, True, True, True, True)
+        assert max_rel(res[0].cpu().numpy(), golden[pre + "gin"]) < 1e-5, i
+        for k in range(4):
+            assert max_rel(res[1 + k].cpu().numpy(), golden[pre + "gparams"][k]) < 2e-4, (i, k)
+
+
+def test_backward_need_mask(bc, golden):
+    pre = "bc4_"
+    N, C, F, h, w, normalize, exact, _ = [int(v) for v in golden[pre + "meta"]]
+    params = [cuda(p) for p in golden[pre + "params"]]
+    integ = bc.integral_image(cuda(golden[pre + "x"]))
+    go = cuda(golden[pre + "go"])
+    rep_h, rep_w = [float(v) for v in golden[pre + "rep"]]
+    full = bc.box_convolution_backward(integ, *params, go, torch.empty(0), rep_h, rep_w,
+                                       bool(normalize), bool(exact), True, True, True, True, True)
+    part = bc.box_convolution_backward(integ, *params, go, torch.empty(0), rep_h, rep_w,
+                                       bool(normalize), bool(exact), False, False, True, False, True)
+    assert part[0].numel() == 0 and part[1].numel() == 0 and part[3].numel() == 0
+    assert torch.equal(part[2], full[2]) and torch.equal(part[4], full[4])
+    only_in = bc.box_convolution_backward(integ, *params, go, torch.empty(0), rep_h, rep_w,
+                                          bool(normalize), bool(exact), True, False, False, False, False)
+    assert all(t.numel() == 0 for t in only_in[1:])
+    assert max_rel(only_in[0].cpu().numpy(), full[0].cpu().numpy()) < 1e-6
+
+
+def test_clip_golden_bitwise(bc, golden):
+    for i in range(int(golden["clip_count"])):
+        pre = "clip%d_" % i
+        C, F, mh, mw, exact = [int(v) for v in golden[pre + "meta"]]
+        rep_h, rep_w = [float(v) for v in golden[pre + "rep"]]
+        ps = [cuda(p) for p in golden[pre + "before"]]
+        bc.clip_parameters(*ps, rep_h, rep_w, mh, mw, bool(exact))
+        got = np.stack([p.cpu().numpy() for p in ps])
+        assert np.array_equal(got, golden[pre + "after"]), i
+
+
+# ------------------------------------------------------------------ module / autograd Function
+def run_module(bc, x, stored, go, max_h, max_w, factor, normalize, exact, train=True):
+    C, F = stored[0].shape
+    m = bc.BoxConv2d(C, F, max_h, max_w, reparametrization_factor=factor, normalize=normalize).cuda()
+    m.exact = exact
+    with torch.no_grad():
+        for p, v in zip((m.x_min, m.x_max, m.y_min, m.y_max), stored):
+            p.copy_(cuda(v))
+    m.train(train)
+    xt = cuda(x).requires_grad_()
+    out = m(xt)
+    out.backward(cuda(go))
+    return (out.detach().cpu().numpy(), xt.grad.cpu().numpy(),
+            [p.grad.cpu().numpy() for p in (m.x_min, m.x_max, m.y_min, m.y_max)], m)
+
+
+def test_function_golden(bc, golden):
+    for i in range(int(golden["bc_count"])):
+        pre = "bc%d_" % i
+        N, C, F, h, w, normalize, exact, _ = [int(v) for v in golden[pre + "meta"]]
+        rep_h, rep_w = [float(v) for v in golden[pre + "rep"]]
+        # stored = pixels / rep would not round-trip bit-exactly; call the Function with rep = 1
+        # on pixel parameters and scale the parameter gradients like the reference does
+        params = [cuda(p).requires_grad_() for p in golden[pre + "params"]]
+        x = cuda(golden[pre + "x"]).requires_grad_()
+        out = bc.BoxConvolutionFunction.apply(x, *params, 1.0, 1.0, bool(normalize), bool(exact))
+        out.backward(cuda(golden[pre + "go"]))
+        assert max_rel(out.detach().cpu().numpy(), golden[pre + "out"]) < 1e-5, i
+        assert max_rel(x.grad.cpu().numpy(), golden[pre + "gin"]) < 1e-5, i
+        for k, rep in enumerate((rep_h, rep_h, rep_w, rep_w)):
+            assert max_rel(params[k].grad.cpu().numpy() * np.float32(rep), golden[pre + "gparams"][k]) < 2e-4, (i, k)
+
+
+@pytest.mark.parametrize("cfg", ["cfg1", "cfg2"])
+def test_module_full_config_vs_oracle(bc, cfg):
+    wl = make_workload(cfg)
+    out, gin, gps, m = run_module(bc, wl.x, wl.stored, wl.grad_output, wl.max_h, wl.max_w, 8,
+                                  True, True)
+    # training-mode clip must be the identity for these boxes
+    for p, v in zip((m.x_min, m.x_max, m.y_min, m.y_max), wl.stored):
+        assert np.array_equal(p.detach().cpu().numpy(), v)
+    ref_out, ref_gin, ref_gps = oracle.boxconv2d_forward_backward(
+        wl.x, wl.stored, wl.grad_output, wl.rep_h, wl.rep_w, True, True)
+    assert max_rel(out, ref_out) < TOL_OUT
+    assert max_rel(gin, ref_gin) < TOL_GIN
+    for k in range(4):
+        assert max_rel(gps[k], ref_gps[k]) < TOL_PARAM, k
+
+
+def test_module_cfg3_subset_vs_oracle(bc):
+    wl = make_workload("cfg3", batch=1, planes=4)
+    out, gin, gps, _ = run_module(bc, wl.x, wl.stored, wl.grad_output, wl.max_h, wl.max_w, 8, True, True)
+    ref_out, ref_gin, ref_gps = oracle.boxconv2d_forward_backward(
+        wl.x, wl.stored, wl.grad_output, wl.rep_h, wl.rep_w, True, True)
+    assert max_rel(out, ref_out) < TOL_OUT
+    assert max_rel(gin, ref_gin) < TOL_GIN
+    for k in range(4):
+        assert max_rel(gps[k], ref_gps[k]) < TOL_PARAM, k
+
+
+@pytest.mark.parametrize("normalize,exact", [(True, True), (False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("shape", [(2, 3, 2, 9, 11), (1, 2, 4, 33, 70), (3, 1, 1, 1, 1), (1, 5, 3, 64, 4),
+                                   (2, 2, 3, 40, 131)])
+def test_module_random_shapes_vs_oracle(bc, shape, normalize, exact):
+    N, C, F, h, w = shape
+    rng = np.random.default_rng(h * 1000 + w + 7 * int(normalize) + 13 * int(exact))
+    x = rng.standard_normal((N, C, h, w)).astype(np.float32)
+    go = rng.standard_normal((N, C * F, h, w)).astype(np.float32)
+    lo = 0.3 if exact else 1.2
+    cx = rng.uniform(-h, h, (C, F)); ex = rng.uniform(lo, h / 2 + lo, (C, F))
+    cy = rng.uniform(-w, w, (C, F)); ey = rng.uniform(lo, w / 2 + lo, (C, F))
+    pix = [a.astype(np.float32) for a in (cx - ex, cx + ex, cy - ey, cy + ey)]
+    if h > 1:
+        pix[0][0, 0], pix[1][0, 0] = -3.0 * h, -2.0 * h     # a box wholly outside the image
+    params = [cuda(p).requires_grad_() for p in pix]
+    xt = cuda(x).requires_grad_()
+    out = bc.BoxConvolutionFunction.apply(xt, *params, 1.0, 1.0, normalize, exact)
+    out.backward(cuda(go))
+    integ = oracle.integral_image(x)
+    ref_out = oracle.box_convolution_forward(integ, *pix, normalize, exact)
+    ref = oracle.box_convolution_backward(integ, *pix, go, ref_out, 1.0, 1.0, normalize, exact)
+    assert max_rel(out.detach().cpu().numpy(), ref_out) < TOL_OUT
+    assert max_rel(xt.grad.cpu().numpy(), ref[0]) < TOL_GIN
+    for k in range(4):
+        assert max_rel(params[k].grad.cpu().numpy(), ref[1 + k]) < TOL_PARAM, k
+    if h > 1:
+        assert (out.detach().view(N, C, F, h, w)[:, 0, 0] == 0).all()
+
+
+def test_eval_mode_clips_once_and_matches(bc):
+    wl = make_workload("cfg1", batch=2)
+    m = bc.BoxConv2d(16, 4, 64, 64).cuda()
+    with torch.no_grad():
+        m.x_min.fill_(0.2)
+        m.x_max.fill_(0.1)        # negative size: the clip must repair it
+    m.eval()
+    assert (m.x_max > m.x_min).all()
+    with torch.no_grad():
+        y = m(cuda(wl.x))
+    assert y.shape == (2, 64, 64, 64) and torch.isfinite(y).all()
+
+
+# ------------------------------------------------------------------ size-independent properties
+@pytest.mark.parametrize("cfg", ["cfg2", "cfg3"])
+def test_adjointness_and_linearity_full_size(bc, cfg):
+    """<grad_output, forward(x)> == <grad_input, x> (the gather and its mirrored-box adjoint),
+    forward is linear in x, and two runs are bit-identical (no atomics anywhere)."""
+    wl = make_workload(cfg)
+    stored = [cuda(p) for p in wl.stored]
+    x = cuda(wl.x).requires_grad_()
+    go = cuda(wl.grad_output)
+
+    def fwd(t):
+        return bc.BoxConvolutionFunction.apply(t, *stored, wl.rep_h, wl.rep_w, True, True)
+
+    out = fwd(x)
+    out.backward(go)
+    lhs = (out.detach().double() * go.double()).sum().item()
+    rhs = (x.grad.double() * x.detach().double()).sum().item()
+    scale = (out.detach().double().abs() * go.double().abs()).sum().item()
+    assert abs(lhs - rhs) < 1e-5 * scale
+    with torch.no_grad():
+        out2 = fwd(x.detach() * 2.0)
+        assert max_rel(out2.cpu().numpy(), (2.0 * out.detach()).cpu().numpy()) < 1e-6
+        out3 = fwd(x.detach())
+        assert torch.equal(out3, out.detach())
+    g1 = x.grad.clone()
+    x.grad = None
+    fwd(x).backward(go)
+    assert torch.equal(g1, x.grad)
+
+
+def test_parameter_gradients_match_finite_differences(bc):
+    """The method of the reference's own test (box_convolution/test.py:276-309): central
+    differences of the loss w.r.t. each stored parameter, on a small smooth case."""
+    rng = np.random.default_rng(11)
+    N, C, F, h, w = 2, 2, 2, 9, 8
+    x = cuda(rng.standard_normal((N, C, h, w)).astype(np.float32))
+    go = cuda(rng.standard_normal((N, C * F, h, w)).astype(np.float32))
+    pix = [np.array(a, np.float32) for a in (
+        [[-2.37, -0.61], [1.44, -3.3]], [[1.58, 2.42], [3.71, 0.36]],
+        [[-1.29, 0.55], [-2.63, -3.45]], [[2.31, 3.62], [0.38, 1.71]])]
+    for normalize in (True, False):
+        params = [cuda(p).requires_grad_() for p in pix]
+        out = bc.BoxConvolutionFunction.apply(x, *params, 1.0, 1.0, normalize, True)
+        out.backward(go)
+        eps = 0.01
+        for k in range(4):
+            for idx in [(0, 0), (1, 1)]:
+                vals = []
+                for sgn in (+1, -1):
+                    pp = [cuda(p.copy()) for p in pix]
+                    pp[k][idx] += sgn * eps
+                    with torch.no_grad():
+                        o = bc.BoxConvolutionFunction.apply(x, *pp, 1.0, 1.0, normalize, True)
+                    vals.append((o.double() * go.double()).sum().item())
+                fd = (vals[0] - vals[1]) / (2 * eps)
+                an = params[k].grad[idx].item()
+                assert abs(fd - an) < 2e-2 * max(1.0, abs(fd)), (normalize, k, idx, fd, an)
+
+
+def test_errors_are_loud(bc):
+    with pytest.raises(RuntimeError):
+        bc.integral_image(torch.zeros(3, 4))                      # CPU tensor: no fallback
+    with pytest.raises(RuntimeError):
+        bc.integral_image(torch.zeros(4, device="cuda"))          # < 2 dims
+    integ = torch.zeros(1, 2, 5, 5, device="cuda")
+    p = torch.zeros(3, 2, device="cuda")
+    with pytest.raises(RuntimeError):
+        bc.box_convolution_forward(integ, p, p, p, p, True, True)  # rows != channels
+    with pytest.raises(RuntimeError):
+        bc.BoxConv2d(2, 2, 8, 8)(torch.zeros(1, 2, 8, 8))          # module on CPU
