@@ -1,0 +1,437 @@
+#!/usr/bin/env python
+"""Benchmark of the BoxConv2d forward+backward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+One step = one training pass of the box block over one batch of synthetic input: parameter
+clip, forward, backward (grad-input and the four parameter gradients) and, on more than one GPU,
+the all-reduce of the packed (4, C, F) parameter gradient.  Each rank works on its own batch of
+the per-GPU shape (weak scaling); `value` is the whole job's output elements per second.
+
+The line printed by rank 0 carries, besides the contract keys:
+  roofline      achieved HBM GB/s of the dominant kernel (algorithmic bytes / mean device time of
+                that kernel, from per-kernel CUDA events recorded by the library during an eager
+                repeat of the timed steps) against the measured copy bandwidth of this pool
+  cpu_baseline  the reference's own CPU code on this machine's host cores (N=1 only)
+  e2e           the same metric from pinned host buffers to host results through the module
+  clocks        SM clock and throttle reasons sampled through NVML while the GPU was busy
+
+`--impl reference` times the reference's CPU implementation of the same step (its compiled
+extension built by oracle/build_ref.py; the plain-C oracle if that build is absent).
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "box-convolutions_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from workloads import CONFIGS, make_workload  # noqa: E402
+
+METRIC = "BoxConv2d fwd+bwd output Gelem/s"
+UNIT = "Gelem/s"
+BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds the 126 MB L2
+# DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
+# profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
+NCU_TRAFFIC = {}
+
+
+def describe(name):
+    N, C, F, h, w = CONFIGS[name][:5]
+    return "%s: BoxConv2d(%d,%d,%d,%d) fwd+bwd, input %dx%dx%dx%d per GPU, fp32, normalize, exact" % (
+        name, C, F, h, w, N, C, h, w)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's CPU code driven the way its autograd Function
+# drives it (box_convolution/box_convolution_function.py:32-65, module.py:216-222)
+# ------------------------------------------------------------------------------------------
+class CpuReference:
+    def __init__(self):
+        from oracle import build_ref, oracle
+        self.ext = build_ref.load_ref()
+        self.kind = "reference" if self.ext is not None else "port"
+        self.oracle = oracle
+        if self.ext is None:
+            oracle.build()
+        self.cores = torch.get_num_threads() if self.ext is not None else 1
+
+    def step(self, wl):
+        """clip -> de-reparametrize -> integral image -> forward -> backward.  Returns seconds."""
+        t0 = time.perf_counter()
+        if self.ext is not None:
+            x = torch.from_numpy(wl.x)
+            go = torch.from_numpy(wl.grad_output)
+            stored = [torch.from_numpy(p.copy()) for p in wl.stored]
+            self.ext.clip_parameters(*stored, wl.rep_h, wl.rep_w, float(wl.max_h), float(wl.max_w), True)
+            actual = [stored[0] * wl.rep_h, stored[1] * wl.rep_h, stored[2] * wl.rep_w, stored[3] * wl.rep_w]
+            integ = self.ext.integral_image(x)
+            out = self.ext.box_convolution_forward(integ, *actual, True, True)
+            self.ext.box_convolution_backward(integ, *actual, go, out, wl.rep_h, wl.rep_w, True, True,
+                                              True, True, True, True, True)
+        else:
+            stored = [p.copy() for p in wl.stored]
+            self.oracle.clip_parameters(*stored, wl.rep_h, wl.rep_w, wl.max_h, wl.max_w, True)
+            self.oracle.boxconv2d_forward_backward(wl.x, stored, wl.grad_output, wl.rep_h, wl.rep_w, True, True)
+        return time.perf_counter() - t0
+
+    def pick_sample(self, name, steps_total, budget_s):
+        """Largest batch (<= the config's) whose `steps_total` steps fit in `budget_s`."""
+        full_n = CONFIGS[name][0]
+        probe = make_workload(name, batch=1)
+        self.step(probe)
+        per_sample = min(self.step(probe) for _ in range(2))
+        n = int(budget_s / max(per_sample * steps_total, 1e-9))
+        return max(1, min(full_n, n))
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    ref = CpuReference()
+    n = ref.pick_sample(args.workload, args.steps + args.warmup, 150.0)
+    wl = make_workload(args.workload, batch=n)
+    for _ in range(args.warmup):
+        ref.step(wl)
+    times = [ref.step(wl) for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    value = wl.outputs / sec / 1e9
+    sample = "batch %d of %d of %s per step, %d steps, mean" % (n, CONFIGS[args.workload][0], args.workload, args.steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": describe(args.workload), "host_threads": ref.cores,
+                   "os_cpu_count": os.cpu_count()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Polls NVML (read-only) for SM clock and throttle reasons of one GPU."""
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting",
+    }
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.samples = []      # (time, sm_mhz, reasons_bitmask, power_w)
+        self.stop_flag = False
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_mhz = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                self.samples.append((time.perf_counter(), mhz, rs, pw))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def summary(self, t0, t1):
+        sel = [s for s in self.samples if t0 <= s[0] <= t1]
+        if not sel:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mask = 0
+        for s in sel:
+            mask |= s[2]
+        return {
+            "sm_mhz": statistics.median(s[1] for s in sel), "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(n for b, n in self.REASONS.items() if mask & b),
+            "samples": len(sel), "power_w_max": max(s[3] for s in sel),
+        }
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def kernel_algorithmic_bytes(kernel, N, C, F, h, w):
+    E, Ei = N * C * h * w, N * C * (h + 1) * (w + 1)
+    return {
+        "integral_image_kernel": None,     # depends on the plane count of the call; not the dominant kernel
+        "forward_global_kernel": 4 * (Ei + F * E),
+        "backward_global_kernel": 4 * (F * Ei + 2 * E),
+        "forward_plane_kernel": 4 * E * (1 + F),
+        "backward_plane_kernel": 4 * E * (F + 2),
+    }.get(kernel)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import box_convolution as bc
+    from box_convolution import _cabi
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    wl = make_workload(args.workload)
+    N, C, F, h, w = wl.shape
+    module = bc.BoxConv2d(C, F, wl.max_h, wl.max_w, reparametrization_factor=8, normalize=True).to(dev)
+    with torch.no_grad():
+        for p, v in zip((module.x_min, module.x_max, module.y_min, module.y_max), wl.stored):
+            p.copy_(torch.from_numpy(v))
+    module.train()
+    params = [module.x_min, module.x_max, module.y_min, module.y_max]
+
+    # distinct inputs per rank and per buffer set (same distribution)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    xs, gos = [], []
+    for s in range(BUFFER_SETS):
+        if s == 0 and rank == 0:
+            xs.append(torch.from_numpy(wl.x).to(dev).requires_grad_())
+            gos.append(torch.from_numpy(wl.grad_output).to(dev))
+        else:
+            xs.append(torch.randn((N, C, h, w), device=dev, generator=gen).requires_grad_())
+            gos.append(torch.randn((N, C * F, h, w), device=dev, generator=gen))
+
+    def step(s):
+        for p in params:
+            p.grad = None
+        xs[s].grad = None
+        out = module(xs[s])
+        out.backward(gos[s])
+        if world > 1:
+            bc.allreduce_box_gradients(module)
+        return out
+
+    # ---- warm-up (eager), then capture one CUDA graph per buffer set
+    for i in range(max(args.warmup, 3)):
+        step(i % BUFFER_SETS)
+    torch.cuda.synchronize()
+    launches_before = _cabi.lib.bc_launch_count()
+    step(0)
+    launches_per_step = _cabi.lib.bc_launch_count() - launches_before
+    torch.cuda.synchronize()
+
+    graphs = None
+    if not args.no_graph:
+        graphs, keep = [], []
+        pool = None
+        for s in range(BUFFER_SETS):
+            g = torch.cuda.CUDAGraph()
+            for p in params:
+                p.grad = None
+            xs[s].grad = None
+            with torch.cuda.graph(g, pool=pool):
+                keep.append(step(s))
+            pool = g.pool()
+            graphs.append(g)
+        for s in range(BUFFER_SETS):
+            graphs[s].replay()
+        torch.cuda.synchronize()
+
+    def run_steps(k):
+        for i in range(k):
+            if graphs is not None:
+                graphs[i % BUFFER_SETS].replay()
+            else:
+                step(i % BUFFER_SETS)
+
+    # ---- the timed region
+    run_steps(max(args.warmup, 3))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start = time.perf_counter()
+    ev0.record()
+    run_steps(args.steps)
+    ev1.record()
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    value = wl.outputs * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-kernel device times: the same steps, eagerly, with the library's event pairs
+    roofline = None
+    eager_ms = None
+    _cabi.check(_cabi.lib.bc_profile_start(args.steps * max(launches_per_step, 1) + 16), "bc_profile_start")
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i % BUFFER_SETS)
+    e1.record()
+    torch.cuda.synchronize()
+    _cabi.lib.bc_profile_stop()
+    t_busy_end = time.perf_counter()
+    eager_ms = e0.elapsed_time(e1) / args.steps
+    import ctypes
+    per_kernel = {}
+    kid, ms = ctypes.c_int(), ctypes.c_float()
+    for i in range(_cabi.lib.bc_profile_count()):
+        _cabi.check(_cabi.lib.bc_profile_get(i, ctypes.byref(kid), ctypes.byref(ms)), "bc_profile_get")
+        per_kernel.setdefault(_cabi.lib.bc_kernel_name(kid.value).decode(), []).append(ms.value)
+    kernels = {k: {"launches": len(v), "mean_us": 1e3 * sum(v) / len(v), "total_ms": sum(v)} for k, v in per_kernel.items()}
+    if kernels:
+        top = max(kernels, key=lambda k: kernels[k]["total_ms"])
+        alg = kernel_algorithmic_bytes(top, N, C, F, h, w)
+        peak, peak_src = measured_peak()
+        if alg is not None:
+            achieved = alg / (kernels[top]["mean_us"] * 1e-6) / 1e9
+            traffic = None
+            if top in NCU_TRAFFIC:
+                b, units = NCU_TRAFFIC[top]
+                traffic = b * (N * C * h * w) / units
+            roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                        "frac": achieved / peak, "traffic": traffic, "algorithmic_bytes": alg,
+                        "mean_us": kernels[top]["mean_us"], "peak_source": peak_src,
+                        "kernels": {k: round(v["mean_us"], 2) for k, v in kernels.items()}}
+
+    # ---- end to end: pinned host buffers in, host results out, through the module
+    e2e = None
+    if not args.skip_e2e:
+        hx = torch.from_numpy(wl.x).pin_memory()
+        hgo = torch.from_numpy(wl.grad_output).pin_memory()
+        hout = torch.empty((N, C * F, h, w), dtype=torch.float32).pin_memory()
+        hgin = torch.empty((N, C, h, w), dtype=torch.float32).pin_memory()
+        hgp = torch.empty((4, C, F), dtype=torch.float32).pin_memory()
+        pipe = bc.HostPipeline(module, N, h, w, chunks=args.e2e_chunks)
+        k_e2e = max(3, min(args.steps, 20))
+        for _ in range(2):
+            pipe.step(hx, hgo, hout, hgin, hgp)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        w0 = time.perf_counter()
+        for _ in range(k_e2e):
+            pipe.step(hx, hgo, hout, hgin, hgp)
+        torch.cuda.synchronize()
+        sec = (time.perf_counter() - w0) / k_e2e
+        if world > 1:
+            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        e2e = {"value": wl.outputs * world / sec / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": hx.numel() * 4 + hgo.numel() * 4,
+               "d2h_bytes_per_step": (hout.numel() + hgin.numel() + hgp.numel()) * 4,
+               "ms_per_step": sec * 1e3, "steps": k_e2e, "chunks": args.e2e_chunks,
+               "api": "box_convolution.HostPipeline.step (BoxConv2d forward/backward per batch chunk, copies on side streams)"}
+        t_busy_end = time.perf_counter()
+
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    clocks = sampler.summary(t_start, t_end)
+    if clocks["samples"] < 3:
+        wider = sampler.summary(t_start, t_busy_end)
+        wider["window"] = "timed region too short for NVML polling; includes the eager and end-to-end legs"
+        clocks = wider
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        ref = CpuReference()
+        n = ref.pick_sample(args.workload, 6, 20.0)
+        sample_wl = make_workload(args.workload, batch=n)
+        ref.step(sample_wl)
+        times = [ref.step(sample_wl) for _ in range(5)]
+        sec = sum(times) / len(times)
+        cpu_baseline = {"value": sample_wl.outputs / sec / 1e9, "unit": UNIT, "cores": ref.cores,
+                        "kind": ref.kind, "os_cpu_count": os.cpu_count(),
+                        "sample": "batch %d of %d of %s, 1 warm-up + 5 steps, mean %.3f s per step" % (
+                            n, N, args.workload, sec)}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": describe(args.workload), "global_batch": N * world,
+                       "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (
+                           BUFFER_SETS, wl.algorithmic_bytes / 1e6),
+                       "launch": "eager" if graphs is None else "cuda graph replay, one graph per buffer set",
+                       "eager_ms_per_step": eager_ms,
+                       "collective": "nccl all_reduce of the packed (4,C,F) parameter gradient" if world > 1 else "none"},
+            "hbm_gbs_step": wl.algorithmic_bytes * world / (ms_per_step * 1e-3) / 1e9,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS))
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=4)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node %d bench.py --gpus %d ..."
+                         % (args.gpus, args.gpus))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py --impl ours needs a GPU: the CUDA library has no CPU fallback")
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,6 +33,21 @@ __device__ __forceinline__ Box load_box(const BoxParams &p, int k)
 // Records a CUDA launch error for bc_last_cuda_error() and maps it to a status code.
 int check_launch(const char *what);
 
+// Kernel ids reported by the profiling aid (bc_profile_get / bc_kernel_name).
+enum KernelId {
+    KID_INTEGRAL = 1, KID_FORWARD_GLOBAL, KID_BACKWARD_GLOBAL, KID_FINISH_PARAM_GRADS, KID_CLIP,
+    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_COUNT
+};
+
+// Put around a kernel launch: counts it and, while profiling is enabled, records a CUDA event on
+// the stream before and after it.
+struct LaunchScope {
+    LaunchScope(int kernel_id, cudaStream_t stream);
+    ~LaunchScope();
+    cudaStream_t stream;
+    int slot;
+};
+
 // ---- launchers (one per translation unit) --------------------------------------------------
 int launch_integral_image(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s);
 

@@ -246,8 +246,11 @@ int launch_finish_param_grads(const float *partials, const BoxParams &bp, int co
 {
     const int warps_per_block = 4;
     const int blocks = (count + warps_per_block - 1) / warps_per_block;
-    finish_param_grads_kernel<<<blocks, warps_per_block * 32, 0, s>>>(
-        partials, bp, count, per_box, normalize, exact, rep_h, rep_w, need_mask, grad_params);
+    {
+        LaunchScope scope(KID_FINISH_PARAM_GRADS, s);
+        finish_param_grads_kernel<<<blocks, warps_per_block * 32, 0, s>>>(
+            partials, bp, count, per_box, normalize, exact, rep_h, rep_w, need_mask, grad_params);
+    }
     return check_launch("finish_param_grads");
 }
 
@@ -260,8 +263,11 @@ int launch_forward_global(const float *integ, const BoxParams &bp, float *out, i
     const int64_t blocks = (int64_t)N * C * F * row_tiles * col_tiles;
     if (blocks == 0) return BC_OK;
     if (blocks > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
-    forward_global_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(integ, bp, out, C, F, h, w, row_tiles,
-                                                                 col_tiles, normalize, exact);
+    {
+        LaunchScope scope(KID_FORWARD_GLOBAL, s);
+        forward_global_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(integ, bp, out, C, F, h, w, row_tiles,
+                                                                     col_tiles, normalize, exact);
+    }
     return check_launch("forward_global");
 }
 
@@ -282,6 +288,8 @@ int launch_backward_global(const float *x, const float *x_integ, const float *go
     if (blocks > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const bool need_params = (need_mask & (BC_NEED_ALL & ~BC_NEED_INPUT)) != 0;
     const bool write_gin = (need_mask & BC_NEED_INPUT) != 0;
+    {
+    LaunchScope scope(KID_BACKWARD_GLOBAL, s);
     if (need_params) {
         backward_global_kernel<true><<<(unsigned)blocks, kThreads, 0, s>>>(
             x, x_integ, go_integ, bp, grad_input, partials, N, C, F, h, w, row_tiles, col_tiles,
@@ -290,6 +298,7 @@ int launch_backward_global(const float *x, const float *x_integ, const float *go
         backward_global_kernel<false><<<(unsigned)blocks, kThreads, 0, s>>>(
             x, x_integ, go_integ, bp, grad_input, partials, N, C, F, h, w, row_tiles, col_tiles,
             normalize, exact, write_gin);
+    }
     }
     int st = check_launch("backward_global");
     if (st != BC_OK || !need_params) return st;

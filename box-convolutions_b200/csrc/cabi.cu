@@ -1,6 +1,9 @@
 // The extern "C" surface declared in include/boxconv_b200.h: argument checks, workspace
 // carving and dispatch to the kernels.  No allocation, no synchronisation.
 #include <stdio.h>
+#include <atomic>
+#include <mutex>
+#include <vector>
 #include <string.h>
 
 #include "bc_common.cuh"
@@ -15,6 +18,30 @@ int check_launch(const char *what)
     if (e == cudaSuccess) return BC_OK;
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
     return BC_ERR_CUDA;
+}
+
+// ---- launch counter and per-kernel event timing
+static std::atomic<uint64_t> g_launches{0};
+static std::mutex g_prof_mutex;
+static bool g_prof_on = false;
+static int g_prof_used = 0;
+struct ProfRecord { int kid; cudaEvent_t a, b; };
+static std::vector<ProfRecord> g_prof;
+
+LaunchScope::LaunchScope(int kernel_id, cudaStream_t s) : stream(s), slot(-1)
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (!g_prof_on) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (!g_prof_on || g_prof_used >= (int)g_prof.size()) return;
+    slot = g_prof_used++;
+    g_prof[slot].kid = kernel_id;
+    cudaEventRecord(g_prof[slot].a, stream);
+}
+
+LaunchScope::~LaunchScope()
+{
+    if (slot >= 0) cudaEventRecord(g_prof[slot].b, stream);
 }
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -203,6 +230,60 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
     return launch_backward_global(input, nullptr, go_integ, bp, reparametrization_h,
                                   reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
                                   need_mask, grad_input, grad_params, partials, stream);
+}
+
+uint64_t bc_launch_count(void) { return g_launches.load(); }
+
+int bc_profile_start(int capacity)
+{
+    if (capacity < 0) return BC_ERR_BAD_SHAPE;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    while ((int)g_prof.size() < capacity) {
+        ProfRecord r{0, nullptr, nullptr};
+        if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess)
+            return check_launch("bc_profile_start");
+        g_prof.push_back(r);
+    }
+    g_prof_used = 0;
+    g_prof_on = true;
+    return BC_OK;
+}
+
+int bc_profile_stop(void)
+{
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_on = false;
+    return BC_OK;
+}
+
+int bc_profile_count(void)
+{
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    return g_prof_used;
+}
+
+int bc_profile_get(int index, int *kernel_id, float *milliseconds)
+{
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (index < 0 || index >= g_prof_used || !kernel_id || !milliseconds) return BC_ERR_BAD_SHAPE;
+    *kernel_id = g_prof[index].kid;
+    if (cudaEventElapsedTime(milliseconds, g_prof[index].a, g_prof[index].b) != cudaSuccess)
+        return check_launch("bc_profile_get");
+    return BC_OK;
+}
+
+const char *bc_kernel_name(int kernel_id)
+{
+    switch (kernel_id) {
+        case KID_INTEGRAL: return "integral_image_kernel";
+        case KID_FORWARD_GLOBAL: return "forward_global_kernel";
+        case KID_BACKWARD_GLOBAL: return "backward_global_kernel";
+        case KID_FINISH_PARAM_GRADS: return "finish_param_grads_kernel";
+        case KID_CLIP: return "clip_kernel";
+        case KID_FORWARD_PLANE: return "forward_plane_kernel";
+        case KID_BACKWARD_PLANE: return "backward_plane_kernel";
+        default: return "unknown";
+    }
 }
 
 }  // extern "C"

@@ -44,6 +44,7 @@ int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int coun
     const double min_size = (double)(exact ? 1.001f : 2.001f);
     const int threads = 128;
     const int blocks = (2 * count + threads - 1) / threads;
+    LaunchScope scope(KID_CLIP, s);
     clip_kernel<<<blocks, threads, 0, s>>>(x_min, x_max, y_min, y_max, count, 1.0 / rep_h, 1.0 / rep_w,
                                            min_size, max_h, max_w);
     return check_launch("clip_parameters");

@@ -139,7 +139,10 @@ int launch_integral_image(const float *in, float *out, int64_t planes, int h, in
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("integral_image: shared memory opt-in");
     }
-    kern<<<(unsigned)planes, kThreads, smem, s>>>(in, out, h, w, tile_rows);
+    {
+        LaunchScope scope(KID_INTEGRAL, s);
+        kern<<<(unsigned)planes, kThreads, smem, s>>>(in, out, h, w, tile_rows);
+    }
     return check_launch("integral_image");
 }
 

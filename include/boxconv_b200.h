@@ -120,6 +120,21 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                           float *grad_input, float *grad_params, void *workspace,
                           size_t workspace_bytes, bc_stream_t stream);
 
+/* ---- measurement aids (no counterpart in the reference) ---------------------------------
+ * bc_launch_count(): kernels launched by this library since it was loaded.
+ * bc_profile_*: while enabled, every kernel launch is bracketed by a pair of CUDA events on the
+ * launching stream, so that a benchmark can read per-kernel device times of a normal run.
+ * Events are host-side objects created by bc_profile_start(); recording must not be enabled
+ * while a stream is being captured into a CUDA graph.  After a device synchronisation,
+ * bc_profile_get(i, ...) returns kernel id and milliseconds of record i;
+ * bc_kernel_name(id) names the kernel. */
+uint64_t bc_launch_count(void);
+int bc_profile_start(int capacity);
+int bc_profile_stop(void);
+int bc_profile_count(void);
+int bc_profile_get(int index, int *kernel_id, float *milliseconds);
+const char *bc_kernel_name(int kernel_id);
+
 #ifdef __cplusplus
 }
 #endif
