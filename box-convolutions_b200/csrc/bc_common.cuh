@@ -62,6 +62,21 @@ int launch_backward_global(const float *x, const float *x_integ, const float *go
                            int h, int w, bool normalize, bool exact, int need_mask,
                            float *grad_input, float *grad_params, float *partials, cudaStream_t s);
 
+int launch_finish_param_grads(const float *partials, const BoxParams &bp, int count, int per_box,
+                              bool normalize, bool exact, float rep_h, float rep_w, int need_mask,
+                              float *grad_params, cudaStream_t s);
+
+// Shared-memory-resident path for small planes (box_plane_smem.cu).
+bool plane_path_fits_forward(int h, int w);
+bool plane_path_fits_backward(int h, int w);
+int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
+                         int w, bool normalize, bool exact, cudaStream_t s);
+// partials: C*F*N*5 floats
+int launch_backward_plane(const float *x, const float *grad_output, const BoxParams &bp, float rep_h,
+                          float rep_w, int N, int C, int F, int h, int w, bool normalize, bool exact,
+                          int need_mask, float *grad_input, float *grad_params, float *partials,
+                          cudaStream_t s);
+
 int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int count, double rep_h,
                 double rep_w, double max_h, double max_w, bool exact, cudaStream_t s);
 

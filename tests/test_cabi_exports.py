@@ -38,6 +38,8 @@ def test_status_strings_and_argument_checks_without_a_gpu():
     assert lib.bc_integral_image(None, None, -1, 4, 5, None) == -2
     assert lib.bc_integral_image(None, None, 0, 4, 5, None) == 0
     assert lib.bc_clip_parameters(None, None, None, None, 4, 1.0, 1.0, 8.0, 8.0, 1, None) == -1
-    assert lib.bc_boxconv2d_forward_workspace(2, 3, 4, 8, 8) > 0
+    assert lib.bc_boxconv2d_forward_workspace(2, 3, 4, 8, 8) == 0          # small planes stay on chip
+    assert lib.bc_boxconv2d_forward_workspace(2, 3, 4, 256, 512) > 0
+    assert lib.bc_box_convolution_backward_workspace(2, 3, 4, 8, 8, 31) > 0
     assert lib.bc_boxconv2d_backward_workspace(2, 3, 4, 8, 8, 31) > 0
     assert lib.bc_boxconv2d_backward_workspace(2, 3, 4, 8, 8, 0) == 0
