@@ -25,6 +25,10 @@
 // registers, the 8 column-group lanes scan row totals with shuffles, warps of the same tile row
 // exchange row totals through shared memory; the same again down the columns.  The block is then
 // stored with the layout above (conflict-free).
+//
+// The kernels are instantiated twice: FAST for planes whose height is a multiple of 8 and width
+// a multiple of 4 with 16-byte aligned tensors (no per-row guards, 128-bit global accesses), and
+// a guarded version for everything else.
 #include "bc_common.cuh"
 
 namespace bc {
@@ -39,7 +43,34 @@ constexpr int kMaxSmem = 200 * 1024;
 
 __host__ __device__ inline int layout_pitch(int w) { return w + 1 + 2 * kPad; }
 __host__ __device__ inline int layout_floats(int h, int w) { return (((h + 1) * layout_pitch(w) + (h >> 3) + 4) + 3) & ~3; }
-__device__ __forceinline__ int row_offset(int a, int k8) { return (a * k8) >> 3; }   // k8 = 8*pitch + 1
+
+// Shared memory is addressed with 32-bit window addresses and explicit ld/st.shared so that the
+// five adjacent taps of a window cost one address computation and five immediate offsets.
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+template <int OFF>
+__device__ __forceinline__ float lds(uint32_t a)
+{
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ void sts(uint32_t a, float v)
+{
+    asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(a), "n"(OFF), "f"(v));
+}
+__device__ __forceinline__ float4 lds128(uint32_t a)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+// Byte address of column -kPad of row a, given the byte address of the image: rows are pitch4
+// bytes apart and row a is skewed by a/8 floats.
+__device__ __forceinline__ uint32_t row_addr(uint32_t base, int a, int pitch4)
+{
+    return base + a * pitch4 + ((a >> 1) & ~3);
+}
 
 inline int warp_tiles(int h, int w) { return ((w + kTile - 1) / kTile) * ((h + kTile - 1) / kTile); }
 
@@ -50,34 +81,62 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
-struct TilePos {
-    int p0, q0, rt, ct;
-    bool valid;
+struct Geometry {
+    int h, w, col_tiles, row_tiles, ntiles, pitch4;
 };
 
-__device__ __forceinline__ TilePos tile_pos(int wt, int ntiles, int col_tiles, int cg, int rg)
+__device__ __forceinline__ Geometry geometry(int h, int w)
+{
+    Geometry g;
+    g.h = h; g.w = w;
+    g.col_tiles = (w + kTile - 1) / kTile;
+    g.row_tiles = (h + kTile - 1) / kTile;
+    g.ntiles = g.col_tiles * g.row_tiles;
+    g.pitch4 = layout_pitch(w) * 4;
+    return g;
+}
+
+struct TilePos {
+    int p0, q0, rt, ct;
+    bool tile;            // the warp tile exists
+    bool active;          // ... and this thread's strip has pixels inside the plane
+};
+
+__device__ __forceinline__ TilePos tile_pos(const Geometry &g, int wt, int cg, int rg)
 {
     TilePos t;
-    t.valid = wt < ntiles;
-    t.rt = wt / col_tiles;
-    t.ct = wt - t.rt * col_tiles;
+    t.rt = wt / g.col_tiles;
+    t.ct = wt - t.rt * g.col_tiles;
     t.p0 = t.rt * kTile + rg * kR;
     t.q0 = t.ct * kTile + cg * kStrip;
+    t.tile = wt < g.ntiles;
+    t.active = t.tile && t.p0 < g.h && t.q0 < g.w;
     return t;
 }
 
-// Builds the padded, skewed integral image of one h x w plane (global memory) in shared memory.
+// Zeroes what never changes in the integral image: row 0 and the left-hand padding (and column
+// 0) of every row.  Followed by the barriers inside build_integral().
+__device__ __forceinline__ void init_integral_padding(float *sI, const Geometry &g)
+{
+    const int pitch = g.pitch4 >> 2;
+    for (int c = threadIdx.x; c < pitch; c += blockDim.x) sI[c] = 0.0f;
+    for (int i = threadIdx.x; i < g.h * (kPad + 1); i += blockDim.x) {
+        const int a = 1 + i / (kPad + 1), c = i - (a - 1) * (kPad + 1);
+        sI[a * pitch + (a >> 3) + c] = 0.0f;
+    }
+}
+
+// Builds the integral image of one h x w plane (global memory) in shared memory: rows 1..h,
+// columns 1..w and the right-hand padding (init_integral_padding() provides the rest).
 // sRow / sCol: scratch for the totals exchanged between warps (kMaxTiles*32 floats each).
 // All threads of the CTA must call it; it ends with a barrier.
-template <int T>
-__device__ __forceinline__ void build_integral(const float *__restrict__ src, float *sI, float *sRow,
-                                               float *sCol, int h, int w, bool vec4)
+template <int T, bool FAST>
+__device__ __forceinline__ void build_integral(const float *__restrict__ src, uint32_t sI32, float *sRow,
+                                               float *sCol, const Geometry &g)
 {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int cg = lane & 7, rg = lane >> 3;
-    const int col_tiles = (w + kTile - 1) / kTile, row_tiles = (h + kTile - 1) / kTile;
-    const int ntiles = col_tiles * row_tiles;
-    const int pitch = layout_pitch(w), k8 = 8 * pitch + 1;
+    const int h = g.h, w = g.w;
 
     float v[T][kR][kStrip];
     TilePos tp[T];
@@ -85,25 +144,25 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, fl
     // ---- load
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        tp[k] = tile_pos(warp + k * nwarps, ntiles, col_tiles, cg, rg);
+        tp[k] = tile_pos(g, warp + k * nwarps, cg, rg);
+        const float *s = src + tp[k].p0 * w + tp[k].q0;
 #pragma unroll
         for (int i = 0; i < kR; ++i) {
-            const int p = tp[k].p0 + i;
-            const bool in = tp[k].valid && p < h && tp[k].q0 < w;
-            if (vec4) {
-                const float4 t = in ? __ldg(reinterpret_cast<const float4 *>(src + p * w + tp[k].q0))
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (FAST) {
+                const float4 t = tp[k].active ? __ldg(reinterpret_cast<const float4 *>(s + i * w))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
                 v[k][i][0] = t.x; v[k][i][1] = t.y; v[k][i][2] = t.z; v[k][i][3] = t.w;
             } else {
+                const bool in = tp[k].active && tp[k].p0 + i < h;
 #pragma unroll
                 for (int m = 0; m < kStrip; ++m)
-                    v[k][i][m] = (in && tp[k].q0 + m < w) ? __ldg(src + p * w + tp[k].q0 + m) : 0.0f;
+                    v[k][i][m] = (in && tp[k].q0 + m < w) ? __ldg(s + i * w + m) : 0.0f;
             }
         }
     }
-    for (int c = tid; c < pitch; c += blockDim.x) sI[c] = 0.0f;          // row 0 with its padding
 
     // ---- along rows: in-thread, across the 8 column-group lanes, across the warps of a tile row
+    float carry[T][kR];
 #pragma unroll
     for (int k = 0; k < T; ++k) {
 #pragma unroll
@@ -116,35 +175,34 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, fl
                 const float u = __shfl_up_sync(0xffffffffu, incl, d, 8);
                 if (cg >= d) incl += u;
             }
-            const float e = incl - own;
-#pragma unroll
-            for (int m = 0; m < kStrip; ++m) v[k][i][m] += e;
-            if (cg == 7 && tp[k].valid) sRow[(tp[k].ct * row_tiles + tp[k].rt) * kTile + rg * kR + i] = incl;
+            carry[k][i] = incl - own;
+            if (cg == 7 && tp[k].tile) sRow[(tp[k].ct * g.row_tiles + tp[k].rt) * kTile + rg * kR + i] = incl;
         }
     }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        if (tp[k].valid) {
+        if (tp[k].tile) {
             for (int c2 = 0; c2 < tp[k].ct; ++c2) {
-                const float4 *s = reinterpret_cast<const float4 *>(sRow + (c2 * row_tiles + tp[k].rt) * kTile + rg * kR);
+                const float4 *s = reinterpret_cast<const float4 *>(sRow + (c2 * g.row_tiles + tp[k].rt) * kTile + rg * kR);
                 const float4 a = s[0], b = s[1];
-                const float add[kR] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int i = 0; i < kR; ++i)
-#pragma unroll
-                    for (int m = 0; m < kStrip; ++m) v[k][i][m] += add[i];
+                carry[k][0] += a.x; carry[k][1] += a.y; carry[k][2] += a.z; carry[k][3] += a.w;
+                carry[k][4] += b.x; carry[k][5] += b.y; carry[k][6] += b.z; carry[k][7] += b.w;
             }
         }
-    }
-
-    // ---- down columns: in-thread, across the 4 row-group lanes, across the warps of a tile column
+        // apply the row carry and run the in-thread column prefix in the same sweep
 #pragma unroll
-    for (int k = 0; k < T; ++k) {
+        for (int m = 0; m < kStrip; ++m) v[k][0][m] += carry[k][0];
 #pragma unroll
         for (int i = 1; i < kR; ++i)
 #pragma unroll
-            for (int m = 0; m < kStrip; ++m) v[k][i][m] += v[k][i - 1][m];
+            for (int m = 0; m < kStrip; ++m) v[k][i][m] += carry[k][i] + v[k][i - 1][m];
+    }
+
+    // ---- down columns: across the 4 row-group lanes, across the warps of a tile column
+    float ccarry[T][kStrip];
+#pragma unroll
+    for (int k = 0; k < T; ++k) {
         float tot[kStrip];
 #pragma unroll
         for (int m = 0; m < kStrip; ++m) {
@@ -154,51 +212,48 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, fl
             if (rg >= 1) incl += u;
             u = __shfl_up_sync(0xffffffffu, incl, 16);
             if (rg >= 2) incl += u;
-            const float e = incl - own;
-#pragma unroll
-            for (int i = 0; i < kR; ++i) v[k][i][m] += e;
+            ccarry[k][m] = incl - own;
             tot[m] = incl;
         }
-        if (rg == 3 && tp[k].valid)
-            *reinterpret_cast<float4 *>(sCol + (tp[k].rt * col_tiles + tp[k].ct) * kTile + cg * kStrip) =
+        if (rg == 3 && tp[k].tile)
+            *reinterpret_cast<float4 *>(sCol + (tp[k].rt * g.col_tiles + tp[k].ct) * kTile + cg * kStrip) =
                 make_float4(tot[0], tot[1], tot[2], tot[3]);
     }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        if (tp[k].valid) {
+        if (tp[k].tile) {
             for (int r2 = 0; r2 < tp[k].rt; ++r2) {
-                const float4 a = *reinterpret_cast<const float4 *>(sCol + (r2 * col_tiles + tp[k].ct) * kTile + cg * kStrip);
-#pragma unroll
-                for (int i = 0; i < kR; ++i) {
-                    v[k][i][0] += a.x; v[k][i][1] += a.y; v[k][i][2] += a.z; v[k][i][3] += a.w;
-                }
+                const float4 a = *reinterpret_cast<const float4 *>(sCol + (r2 * g.col_tiles + tp[k].ct) * kTile + cg * kStrip);
+                ccarry[k][0] += a.x; ccarry[k][1] += a.y; ccarry[k][2] += a.z; ccarry[k][3] += a.w;
             }
         }
     }
 
-    // ---- store rows 1..h with their padding
+    // ---- store rows p0+1 .. p0+8, columns q0+1 .. q0+4, and the right-hand padding
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        if (tp[k].valid && tp[k].q0 < w) {
+        if (tp[k].active) {
             const int q0 = tp[k].q0;
+            // address of column q0 of row a; the +1 column shift is in the immediates
+            const uint32_t col = sI32 + (kPad + q0) * 4;
+            const bool last = q0 + kStrip >= w;
+            const int npad = w - q0;     // padding columns this strip still has to fill (1..4) when `last`
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
                 const int a = tp[k].p0 + i + 1;
-                if (a <= h) {
-                    float *row = sI + row_offset(a, k8) + kPad;
-                    // columns q0+1 .. q0+4; past the plane's last column the running value is
-                    // I[a][w], which is exactly what the right-hand padding has to hold
-#pragma unroll
-                    for (int m = 0; m < kStrip; ++m) row[q0 + 1 + m] = v[k][i][m];
-                    if (q0 + kStrip >= w) {
-#pragma unroll
-                        for (int m = 0; m < kPad; ++m)
-                            if (q0 + kStrip + 1 + m <= w + kPad) row[q0 + kStrip + 1 + m] = v[k][i][kStrip - 1];
-                    }
-                    if (q0 == 0) {
-#pragma unroll
-                        for (int m = -kPad; m <= 0; ++m) row[m] = 0.0f;
+                if (FAST || a <= h) {
+                    const uint32_t ra = row_addr(col, a, g.pitch4);
+                    const float x0 = v[k][i][0] + ccarry[k][0], x1 = v[k][i][1] + ccarry[k][1];
+                    const float x2 = v[k][i][2] + ccarry[k][2], x3 = v[k][i][3] + ccarry[k][3];
+                    // past the plane's last column the running value is I[a][w], which is exactly
+                    // what the right-hand padding has to hold
+                    sts<4>(ra, x0); sts<8>(ra, x1); sts<12>(ra, x2); sts<16>(ra, x3);
+                    if (last) {
+                        sts<20>(ra, x3);
+                        if (npad > 1) sts<24>(ra, x3);
+                        if (npad > 2) sts<28>(ra, x3);
+                        if (npad > 3) sts<32>(ra, x3);
                     }
                 }
             }
@@ -207,56 +262,70 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, fl
     __syncthreads();
 }
 
-// Column window starts of a strip (clamped: see the layout note on top).
-__device__ __forceinline__ void window_bases(const BoxTaps &t, int q0, int w, int &bl, int &bh)
+// What a thread needs to read the tap rows of its strip for one box: the byte address of the
+// lo-side window in row 0 (without skew) and the distance to the hi-side window.
+struct Windows {
+    uint32_t lo;      // address of column clamp(q0+lo_c-1) of row 0
+    uint32_t dhi;     // byte distance from the lo window to the hi window
+};
+
+__device__ __forceinline__ Windows windows(uint32_t sI32, const BoxTaps &t, int q0, int w)
 {
-    bl = clampi(q0 + t.lo_c - 1, -kPad, w);
-    bh = clampi(q0 + t.hi_c, -kPad, w);
+    const int bl = min(max(q0 + t.lo_c - 1, -kPad), w);
+    const int bh = min(max(q0 + t.hi_c, -kPad), w);
+    Windows o;
+    o.lo = sI32 + (kPad + bl) * 4;
+    o.dhi = (uint32_t)((bh - bl) * 4);
+    return o;
 }
 
-struct TapRow {      // column-combined value of one tap row, per column of the strip
+struct ColW {         // column weights of a box: (1-f_hi), f_hi, (1-f_lo), f_lo
+    float wh, fh, wl, fl;
+};
+
+struct TapRow {       // column-combined value of one tap row, per column of the strip
     float d[kStrip];
 };
-struct TapRowE {     // ... plus the one-column strips outside the box on either side
+struct TapRowE {      // ... plus the one-column strips outside the box on either side
     float d[kStrip], e_lo[kStrip], e_hi[kStrip];
 };
 
-__device__ __forceinline__ TapRow load_tap_row(const float *sIp, int a, int k8, int bl, int bh, float wl,
-                                               float fl, float wh, float fh)
+__device__ __forceinline__ TapRow load_tap_row(const Windows &wn, int a, int h, int pitch4, const ColW &cw)
 {
-    const float *r = sIp + row_offset(a, k8);
-    const float *pl = r + bl, *ph = r + bh;
-    float vl[kStrip + 1], vh[kStrip + 1];
-#pragma unroll
-    for (int m = 0; m <= kStrip; ++m) { vl[m] = pl[m]; vh[m] = ph[m]; }
+    const uint32_t al = row_addr(wn.lo, min(max(a, 0), h), pitch4);
+    const uint32_t ah = al + wn.dhi;
+    const float l0 = lds<0>(al), l1 = lds<4>(al), l2 = lds<8>(al), l3 = lds<12>(al), l4 = lds<16>(al);
+    const float h0 = lds<0>(ah), h1 = lds<4>(ah), h2 = lds<8>(ah), h3 = lds<12>(ah), h4 = lds<16>(ah);
     TapRow o;
-#pragma unroll
-    for (int m = 0; m < kStrip; ++m) o.d[m] = wh * vh[m] + fh * vh[m + 1] - wl * vl[m + 1] - fl * vl[m];
+    o.d[0] = cw.wh * h0 + cw.fh * h1 - cw.wl * l1 - cw.fl * l0;
+    o.d[1] = cw.wh * h1 + cw.fh * h2 - cw.wl * l2 - cw.fl * l1;
+    o.d[2] = cw.wh * h2 + cw.fh * h3 - cw.wl * l3 - cw.fl * l2;
+    o.d[3] = cw.wh * h3 + cw.fh * h4 - cw.wl * l4 - cw.fl * l3;
     return o;
 }
 
-__device__ __forceinline__ TapRowE load_tap_row_e(const float *sIp, int a, int k8, int bl, int bh, float wl,
-                                                  float fl, float wh, float fh)
+__device__ __forceinline__ TapRowE load_tap_row_e(const Windows &wn, int a, int h, int pitch4, const ColW &cw)
 {
-    const float *r = sIp + row_offset(a, k8);
-    const float *pl = r + bl, *ph = r + bh;
-    float vl[kStrip + 1], vh[kStrip + 1];
-#pragma unroll
-    for (int m = 0; m <= kStrip; ++m) { vl[m] = pl[m]; vh[m] = ph[m]; }
+    const uint32_t al = row_addr(wn.lo, min(max(a, 0), h), pitch4);
+    const uint32_t ah = al + wn.dhi;
+    const float l0 = lds<0>(al), l1 = lds<4>(al), l2 = lds<8>(al), l3 = lds<12>(al), l4 = lds<16>(al);
+    const float h0 = lds<0>(ah), h1 = lds<4>(ah), h2 = lds<8>(ah), h3 = lds<12>(ah), h4 = lds<16>(ah);
     TapRowE o;
-#pragma unroll
-    for (int m = 0; m < kStrip; ++m) {
-        o.d[m] = wh * vh[m] + fh * vh[m + 1] - wl * vl[m + 1] - fl * vl[m];
-        o.e_lo[m] = vl[m + 1] - vl[m];
-        o.e_hi[m] = vh[m + 1] - vh[m];
-    }
+    o.e_lo[0] = l1 - l0; o.e_lo[1] = l2 - l1; o.e_lo[2] = l3 - l2; o.e_lo[3] = l4 - l3;
+    o.e_hi[0] = h1 - h0; o.e_hi[1] = h2 - h1; o.e_hi[2] = h3 - h2; o.e_hi[3] = h4 - h3;
+    // d = (1-f_hi) h[m] + f_hi h[m+1] - (1-f_lo) l[m+1] - f_lo l[m]
+    //   = (h[m] - l[m+1]) + f_hi e_hi[m] + f_lo e_lo[m]
+    o.d[0] = (h0 - l1) + cw.fh * o.e_hi[0] + cw.fl * o.e_lo[0];
+    o.d[1] = (h1 - l2) + cw.fh * o.e_hi[1] + cw.fl * o.e_lo[1];
+    o.d[2] = (h2 - l3) + cw.fh * o.e_hi[2] + cw.fl * o.e_lo[2];
+    o.d[3] = (h3 - l4) + cw.fh * o.e_hi[3] + cw.fl * o.e_lo[3];
     return o;
 }
 
-template <int T>
+template <int T, bool FAST>
 __global__ void __launch_bounds__(256)
 forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restrict__ out, int C, int F,
-                     int h, int w, int fsplit, bool normalize, bool exact, bool vec4)
+                     int h, int w, int fsplit, bool normalize, bool exact)
 {
     extern __shared__ float4 smem4[];
     float *sI = reinterpret_cast<float *>(smem4);
@@ -267,46 +336,44 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
     const int part = blockIdx.x % fsplit;
     const int c = (int)(nc % C);
     const int f_begin = (F * part) / fsplit, f_end = (F * (part + 1)) / fsplit;
+    const Geometry g = geometry(h, w);
+    const uint32_t sI32 = smem_u32(sI);
 
-    build_integral<T>(x + nc * (int64_t)h * w, sI, sRow, sCol, h, w, vec4);
+    init_integral_padding(sI, g);
+    build_integral<T, FAST>(x + nc * (int64_t)h * w, sI32, sRow, sCol, g);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int cg = lane & 7, rg = lane >> 3;
-    const int col_tiles = (w + kTile - 1) / kTile, row_tiles = (h + kTile - 1) / kTile;
-    const int ntiles = col_tiles * row_tiles;
-    const int k8 = 8 * layout_pitch(w) + 1;
-    const float *sIp = sI + kPad;
 
     for (int f = f_begin; f < f_end; ++f) {
         const Box box = load_box(bp, c * F + f);
         const BoxTaps t = taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact);
-        const float wl = 1.0f - t.f_lo_c, wh = 1.0f - t.f_hi_c;
+        const ColW cw = {1.0f - t.f_hi_c, t.f_hi_c, 1.0f - t.f_lo_c, t.f_lo_c};
         float *o = out + (nc * F + f) * (int64_t)h * w;
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(warp + k * nwarps, ntiles, col_tiles, cg, rg);
-            if (!tp.valid || tp.q0 >= w || tp.p0 >= h) continue;
-            int bl, bh;
-            window_bases(t, tp.q0, w, bl, bh);
-            TapRow ra = load_tap_row(sIp, clampi(tp.p0 + t.lo_r - 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-            TapRow rc = load_tap_row(sIp, clampi(tp.p0 + t.hi_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
+            if (!tp.active) continue;
+            const Windows wn = windows(sI32, t, tp.q0, w);
+            TapRow ra = load_tap_row(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
+            TapRow rc = load_tap_row(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
+            float *dst = o + tp.p0 * w + tp.q0;
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
                 const int p = tp.p0 + i;
-                if (p < h) {
-                    const TapRow rb = load_tap_row(sIp, clampi(p + t.lo_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-                    const TapRow rd = load_tap_row(sIp, clampi(p + t.hi_r + 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+                if (FAST || p < h) {
+                    const TapRow rb = load_tap_row(wn, p + t.lo_r, h, g.pitch4, cw);
+                    const TapRow rd = load_tap_row(wn, p + t.hi_r + 1, h, g.pitch4, cw);
                     float v[kStrip];
 #pragma unroll
                     for (int m = 0; m < kStrip; ++m)
                         v[m] = combine_rows(ra.d[m], rb.d[m], rc.d[m], rd.d[m], t.f_lo_r, t.f_hi_r) * t.scale;
-                    float *dst = o + p * w + tp.q0;
-                    if (vec4) {
-                        *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                    if (FAST) {
+                        *reinterpret_cast<float4 *>(dst + i * w) = make_float4(v[0], v[1], v[2], v[3]);
                     } else {
 #pragma unroll
                         for (int m = 0; m < kStrip; ++m)
-                            if (tp.q0 + m < w) dst[m] = v[m];
+                            if (tp.q0 + m < w) dst[i * w + m] = v[m];
                     }
                     ra = rb;
                     rc = rd;
@@ -318,11 +385,11 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
 
 // T = warp tiles per warp: grad-input accumulators are registers, so the number of strips a
 // thread owns is a compile-time constant.
-template <int T, bool NEED_PARAMS>
+template <int T, bool FAST, bool NEED_PARAMS>
 __global__ void __launch_bounds__(512)
 backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ grad_output, BoxParams bp,
                       float *__restrict__ grad_input, float *__restrict__ partials, int N, int C, int F,
-                      int h, int w, bool normalize, bool exact, bool vec4, bool write_gin)
+                      int h, int w, bool normalize, bool exact, bool write_gin)
 {
     extern __shared__ float4 smem4[];
     float *sI = reinterpret_cast<float *>(smem4);          // integral(grad_output plane)
@@ -335,15 +402,14 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     const int c = (int)(nc % C), n = (int)(nc / C);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int cg = lane & 7, rg = lane >> 3;
-    const int col_tiles = (w + kTile - 1) / kTile, row_tiles = (h + kTile - 1) / kTile;
-    const int ntiles = col_tiles * row_tiles;
-    const int k8 = 8 * layout_pitch(w) + 1;
-    const float *sIp = sI + kPad;
+    const Geometry g = geometry(h, w);
+    const uint32_t sI32 = smem_u32(sI), sX32 = smem_u32(sX);
     const int npix = h * w;
 
+    init_integral_padding(sI, g);
     if (NEED_PARAMS) {
         const float *xp = x + nc * (int64_t)npix;
-        if (vec4) {
+        if (FAST) {
             for (int i = tid; i < (npix >> 2); i += blockDim.x)
                 reinterpret_cast<float4 *>(sX)[i] = __ldg(reinterpret_cast<const float4 *>(xp) + i);
         } else {
@@ -362,41 +428,41 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     for (int f = 0; f < F; ++f) {
         // (the barrier that ends the previous iteration protects sI, sRow, sCol)
         const float *gplane = grad_output + (nc * F + f) * (int64_t)npix;
-        build_integral<T>(gplane, sI, sRow, sCol, h, w, vec4);
+        build_integral<T, FAST>(gplane, sI32, sRow, sCol, g);
         if (f + 1 < F && cg == 0) {
             // pull the next grad_output plane towards L2 while this one is gathered
 #pragma unroll
             for (int k = 0; k < T; ++k) {
-                const TilePos tp = tile_pos(warp + k * nwarps, ntiles, col_tiles, cg, rg);
+                const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
 #pragma unroll
                 for (int i = 0; i < kR; ++i)
-                    if (tp.valid && tp.p0 + i < h && tp.q0 < w)
+                    if (tp.active && tp.p0 + i < h)
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(gplane + npix + (tp.p0 + i) * w + tp.q0));
             }
         }
 
         const Box box = load_box(bp, c * F + f);
         const BoxTaps t = taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact);
-        const float wl = 1.0f - t.f_lo_c, wh = 1.0f - t.f_hi_c;
+        const ColW cw = {1.0f - t.f_hi_c, t.f_hi_c, 1.0f - t.f_lo_c, t.f_lo_c};
         ParamSums sums = {0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(warp + k * nwarps, ntiles, col_tiles, cg, rg);
-            if (tp.valid && tp.q0 < w && tp.p0 < h) {
-                int bl, bh;
-                window_bases(t, tp.q0, w, bl, bh);
+            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
+            if (tp.active) {
+                const Windows wn = windows(sI32, t, tp.q0, w);
                 if (NEED_PARAMS) {
-                    TapRowE ra = load_tap_row_e(sIp, clampi(tp.p0 + t.lo_r - 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-                    TapRowE rc = load_tap_row_e(sIp, clampi(tp.p0 + t.hi_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+                    TapRowE ra = load_tap_row_e(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
+                    TapRowE rc = load_tap_row_e(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
+                    const uint32_t xa = sX32 + (tp.p0 * w + tp.q0) * 4;
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
                         const int p = tp.p0 + i;
-                        if (p < h) {
-                            const TapRowE rb = load_tap_row_e(sIp, clampi(p + t.lo_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-                            const TapRowE rd = load_tap_row_e(sIp, clampi(p + t.hi_r + 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+                        if (FAST || p < h) {
+                            const TapRowE rb = load_tap_row_e(wn, p + t.lo_r, h, g.pitch4, cw);
+                            const TapRowE rd = load_tap_row_e(wn, p + t.hi_r + 1, h, g.pitch4, cw);
                             float xv[kStrip];
-                            if (vec4) {
-                                const float4 v = *reinterpret_cast<const float4 *>(sX + p * w + tp.q0);
+                            if (FAST) {
+                                const float4 v = lds128(xa + i * w * 4);
                                 xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
                             } else {
 #pragma unroll
@@ -406,29 +472,29 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
                             for (int m = 0; m < kStrip; ++m) {
                                 const float top = rb.d[m] - ra.d[m];
                                 const float bot = rd.d[m] - rc.d[m];
-                                const float g = (rc.d[m] - rb.d[m]) + t.f_hi_r * bot + t.f_lo_r * top;
+                                const float gg = (rc.d[m] - rb.d[m]) + t.f_hi_r * bot + t.f_lo_r * top;
                                 const float sl = combine_rows(ra.e_lo[m], rb.e_lo[m], rc.e_lo[m], rd.e_lo[m], t.f_lo_r, t.f_hi_r);
                                 const float sr = combine_rows(ra.e_hi[m], rb.e_hi[m], rc.e_hi[m], rd.e_hi[m], t.f_lo_r, t.f_hi_r);
-                                sums.s_out += xv[m] * g;
+                                sums.s_out += xv[m] * gg;
                                 sums.s_top += xv[m] * top;
                                 sums.s_bot += xv[m] * bot;
                                 sums.s_left += xv[m] * sl;
                                 sums.s_right += xv[m] * sr;
-                                gin[k][i][m] += g * t.scale;
+                                gin[k][i][m] += gg * t.scale;
                             }
                             ra = rb;
                             rc = rd;
                         }
                     }
                 } else {
-                    TapRow ra = load_tap_row(sIp, clampi(tp.p0 + t.lo_r - 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-                    TapRow rc = load_tap_row(sIp, clampi(tp.p0 + t.hi_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+                    TapRow ra = load_tap_row(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
+                    TapRow rc = load_tap_row(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
                         const int p = tp.p0 + i;
-                        if (p < h) {
-                            const TapRow rb = load_tap_row(sIp, clampi(p + t.lo_r, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
-                            const TapRow rd = load_tap_row(sIp, clampi(p + t.hi_r + 1, 0, h), k8, bl, bh, wl, t.f_lo_c, wh, t.f_hi_c);
+                        if (FAST || p < h) {
+                            const TapRow rb = load_tap_row(wn, p + t.lo_r, h, g.pitch4, cw);
+                            const TapRow rd = load_tap_row(wn, p + t.hi_r + 1, h, g.pitch4, cw);
 #pragma unroll
                             for (int m = 0; m < kStrip; ++m)
                                 gin[k][i][m] += combine_rows(ra.d[m], rb.d[m], rc.d[m], rd.d[m], t.f_lo_r, t.f_hi_r) * t.scale;
@@ -451,7 +517,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
         __syncthreads();      // gathers of this filter are done: sI may be rebuilt; red[] is complete
         if (NEED_PARAMS && tid < kNumSums) {
             float s = 0.0f;
-            for (int g = 0; g < nwarps; ++g) s += red[g][tid];
+            for (int j = 0; j < nwarps; ++j) s += red[j][tid];
             partials[((int64_t)(c * F + f) * N + n) * kNumSums + tid] = s;
         }
         // red[] is next written after the barriers inside the next build_integral
@@ -461,20 +527,17 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
         float *gi = grad_input + nc * (int64_t)npix;
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(warp + k * nwarps, ntiles, col_tiles, cg, rg);
-            if (tp.valid && tp.q0 < w) {
+            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
+            if (tp.active) {
+                float *dst = gi + tp.p0 * w + tp.q0;
 #pragma unroll
                 for (int i = 0; i < kR; ++i) {
-                    const int p = tp.p0 + i;
-                    if (p < h) {
-                        float *dst = gi + p * w + tp.q0;
-                        if (vec4) {
-                            *reinterpret_cast<float4 *>(dst) = make_float4(gin[k][i][0], gin[k][i][1], gin[k][i][2], gin[k][i][3]);
-                        } else {
+                    if (FAST) {
+                        *reinterpret_cast<float4 *>(dst + i * w) = make_float4(gin[k][i][0], gin[k][i][1], gin[k][i][2], gin[k][i][3]);
+                    } else if (tp.p0 + i < h) {
 #pragma unroll
-                            for (int m = 0; m < kStrip; ++m)
-                                if (tp.q0 + m < w) dst[m] = gin[k][i][m];
-                        }
+                        for (int m = 0; m < kStrip; ++m)
+                            if (tp.q0 + m < w) dst[i * w + m] = gin[k][i][m];
                     }
                 }
             }
@@ -490,6 +553,8 @@ int opt_in_smem(K kernel, size_t bytes)
         return check_launch("shared memory opt-in");
     return BC_OK;
 }
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
 
@@ -508,25 +573,24 @@ int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N,
                          int w, bool normalize, bool exact, cudaStream_t s)
 {
     const int64_t planes = (int64_t)N * C;
-    // split the filters of a plane over several CTAs while there are too few planes to balance
-    // 148 SMs; every part rebuilds the integral image (cheap next to the gathers, and the second
-    // read of the plane comes from L2)
+    // Split the filters of a plane over two CTAs when there are too few planes to balance 148 SMs
+    // (each part rebuilds the integral image; the second read of the plane comes from L2).
     int fsplit = 1;
-    while (fsplit < F && planes * fsplit < 148 * 12 && F % (fsplit * 2) == 0) fsplit *= 2;
+    if (F % 2 == 0 && planes < 148 * 6) fsplit = 2;
     if (planes * fsplit > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const size_t smem = (size_t)layout_floats(h, w) * sizeof(float);
     const int tiles = warp_tiles(h, w);
     const int T = tiles > 16 ? 4 : (tiles > 8 ? 2 : 1);
     const int warps = (tiles + T - 1) / T;
-    auto kern = T == 1 ? forward_plane_kernel<1> : (T == 2 ? forward_plane_kernel<2> : forward_plane_kernel<4>);
+    const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(out);
+    void (*kern)(const float *, BoxParams, float *, int, int, int, int, int, bool, bool);
+    if (fast) kern = T == 1 ? forward_plane_kernel<1, true> : (T == 2 ? forward_plane_kernel<2, true> : forward_plane_kernel<4, true>);
+    else kern = T == 1 ? forward_plane_kernel<1, false> : (T == 2 ? forward_plane_kernel<2, false> : forward_plane_kernel<4, false>);
     int st = opt_in_smem(kern, smem);
     if (st != BC_OK) return st;
-    const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
-                      ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
     {
         LaunchScope scope(KID_FORWARD_PLANE, s);
-        kern<<<(unsigned)(planes * fsplit), warps * 32, smem, s>>>(x, bp, out, C, F, h, w, fsplit, normalize,
-                                                                    exact, vec4);
+        kern<<<(unsigned)(planes * fsplit), warps * 32, smem, s>>>(x, bp, out, C, F, h, w, fsplit, normalize, exact);
     }
     return check_launch("forward_plane");
 }
@@ -544,17 +608,22 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     const int tiles = warp_tiles(h, w);
     const int T = tiles > 8 ? 2 : 1;
     const int warps = (tiles + T - 1) / T;
-    const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
-                      ((reinterpret_cast<uintptr_t>(grad_output) & 15) == 0) &&
-                      (!write_gin || (reinterpret_cast<uintptr_t>(grad_input) & 15) == 0);
-    auto kern = T == 1 ? (need_params ? backward_plane_kernel<1, true> : backward_plane_kernel<1, false>)
-                       : (need_params ? backward_plane_kernel<2, true> : backward_plane_kernel<2, false>);
+    const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(grad_output) &&
+                      (!write_gin || aligned16(grad_input));
+    void (*kern)(const float *, const float *, BoxParams, float *, float *, int, int, int, int, int, bool, bool, bool);
+    if (fast) {
+        kern = T == 1 ? (need_params ? backward_plane_kernel<1, true, true> : backward_plane_kernel<1, true, false>)
+                      : (need_params ? backward_plane_kernel<2, true, true> : backward_plane_kernel<2, true, false>);
+    } else {
+        kern = T == 1 ? (need_params ? backward_plane_kernel<1, false, true> : backward_plane_kernel<1, false, false>)
+                      : (need_params ? backward_plane_kernel<2, false, true> : backward_plane_kernel<2, false, false>);
+    }
     int st = opt_in_smem(kern, smem);
     if (st != BC_OK) return st;
     {
         LaunchScope scope(KID_BACKWARD_PLANE, s);
-        kern<<<(unsigned)planes, warps * 32, smem, s>>>(x, grad_output, bp, grad_input, partials, N, C, F, h,
-                                                       w, normalize, exact, vec4, write_gin);
+        kern<<<(unsigned)planes, warps * 32, smem, s>>>(x, grad_output, bp, grad_input, partials, N, C, F, h, w,
+                                                       normalize, exact, write_gin);
     }
     st = check_launch("backward_plane");
     if (st != BC_OK || !need_params) return st;
