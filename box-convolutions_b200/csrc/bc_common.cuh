@@ -67,8 +67,8 @@ int launch_finish_param_grads(const float *partials, const BoxParams &bp, int co
                               float *grad_params, cudaStream_t s);
 
 // Shared-memory-resident path for small planes (box_plane_smem.cu).
-bool plane_path_fits_forward(int h, int w);
-bool plane_path_fits_backward(int h, int w);
+bool plane_path_fits_forward(int F, int h, int w);
+bool plane_path_fits_backward(int F, int h, int w);
 int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
                          int w, bool normalize, bool exact, cudaStream_t s);
 // partials: C*F*N*5 floats

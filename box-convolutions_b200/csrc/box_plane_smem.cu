@@ -65,6 +65,38 @@ __device__ __forceinline__ float4 lds128(uint32_t a)
     asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
     return v;
 }
+// Two floats in one 64-bit register for the packed fp32 pipe of sm_100 (add/sub/mul/fma.f32x2):
+// one issue slot does the arithmetic of two lanes.  .x is the low half.
+typedef unsigned long long f2_t;
+__device__ __forceinline__ f2_t pack2(float lo, float hi)
+{
+    f2_t r;
+    asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f2_t v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0,%1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2_t fma2(f2_t a, f2_t b, f2_t c)
+{
+    f2_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f2_t mul2(f2_t a, f2_t b)
+{
+    f2_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f2_t sub2(f2_t a, f2_t b)
+{
+    f2_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 // Byte address of column -kPad of row a, given the byte address of the image: rows are pitch4
 // bytes apart and row a is skewed by a/8 floats.
 __device__ __forceinline__ uint32_t row_addr(uint32_t base, int a, int pitch4)
@@ -239,11 +271,13 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, ui
             const uint32_t col = sI32 + (kPad + q0) * 4;
             const bool last = q0 + kStrip >= w;
             const int npad = w - q0;     // padding columns this strip still has to fill (1..4) when `last`
+            const uint32_t ra0 = row_addr(col, tp[k].p0 + 1, g.pitch4);
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
                 const int a = tp[k].p0 + i + 1;
                 if (FAST || a <= h) {
-                    const uint32_t ra = row_addr(col, a, g.pitch4);
+                    // p0 is a multiple of 8, so only the last of the 8 rows moves to the next skew
+                    const uint32_t ra = ra0 + i * g.pitch4 + (i == kR - 1 ? 4 : 0);
                     const float x0 = v[k][i][0] + ccarry[k][0], x1 = v[k][i][1] + ccarry[k][1];
                     const float x2 = v[k][i][2] + ccarry[k][2], x3 = v[k][i][3] + ccarry[k][3];
                     // past the plane's last column the running value is I[a][w], which is exactly
@@ -262,64 +296,111 @@ __device__ __forceinline__ void build_integral(const float *__restrict__ src, ui
     __syncthreads();
 }
 
-// What a thread needs to read the tap rows of its strip for one box: the byte address of the
-// lo-side window in row 0 (without skew) and the distance to the hi-side window.
-struct Windows {
-    uint32_t lo;      // address of column clamp(q0+lo_c-1) of row 0
+// Per-CTA table of the boxes this CTA works with (shared memory, filled once before the first
+// barrier): integer tap offsets, fractions and scale of BoxTaps, padded to three 16-byte words.
+constexpr int kMaxFilters = 32;
+constexpr int kTapWords = 12;
+
+__device__ __forceinline__ void store_taps(float *tab, const BoxTaps &t)
+{
+    int *ti = reinterpret_cast<int *>(tab);
+    ti[0] = t.lo_r; ti[1] = t.hi_r; ti[2] = t.lo_c; ti[3] = t.hi_c;
+    tab[4] = t.f_lo_r; tab[5] = t.f_hi_r; tab[6] = t.f_lo_c; tab[7] = t.f_hi_c;
+    tab[8] = t.scale; tab[9] = 0.f; tab[10] = 0.f; tab[11] = 0.f;
+}
+
+__device__ __forceinline__ BoxTaps load_taps(const float *tab)
+{
+    const float4 a = *reinterpret_cast<const float4 *>(tab);
+    const float4 b = *reinterpret_cast<const float4 *>(tab + 4);
+    BoxTaps t;
+    t.lo_r = __float_as_int(a.x); t.hi_r = __float_as_int(a.y);
+    t.lo_c = __float_as_int(a.z); t.hi_c = __float_as_int(a.w);
+    t.f_lo_r = b.x; t.f_hi_r = b.y; t.f_lo_c = b.z; t.f_hi_c = b.w;
+    t.scale = tab[8];
+    return t;
+}
+
+// Address arithmetic of a strip walk.  Tap rows are read in (lo, hi) pairs: the row on the lo
+// side of the box and the row on its hi side are fetched together and their values kept as the
+// two halves of packed registers, so the column combination runs on the f32x2 pipe.
+struct Walk {
+    uint32_t lo;      // address of the lo-side window (column clamp(q0+lo_c-1)) in row 0, no skew
     uint32_t dhi;     // byte distance from the lo window to the hi window
+    int pitch4, h;
 };
 
-__device__ __forceinline__ Windows windows(uint32_t sI32, const BoxTaps &t, int q0, int w)
+__device__ __forceinline__ Walk make_walk(uint32_t sI32, const BoxTaps &t, int q0, const Geometry &g)
 {
-    const int bl = min(max(q0 + t.lo_c - 1, -kPad), w);
-    const int bh = min(max(q0 + t.hi_c, -kPad), w);
-    Windows o;
+    const int bl = min(max(q0 + t.lo_c - 1, -kPad), g.w);
+    const int bh = min(max(q0 + t.hi_c, -kPad), g.w);
+    Walk o;
     o.lo = sI32 + (kPad + bl) * 4;
     o.dhi = (uint32_t)((bh - bl) * 4);
+    o.pitch4 = g.pitch4;
+    o.h = g.h;
     return o;
 }
 
-struct ColW {         // column weights of a box: (1-f_hi), f_hi, (1-f_lo), f_lo
-    float wh, fh, wl, fl;
-};
-
-struct TapRow {       // column-combined value of one tap row, per column of the strip
-    float d[kStrip];
-};
-struct TapRowE {      // ... plus the one-column strips outside the box on either side
-    float d[kStrip], e_lo[kStrip], e_hi[kStrip];
-};
-
-__device__ __forceinline__ TapRow load_tap_row(const Windows &wn, int a, int h, int pitch4, const ColW &cw)
+__device__ __forceinline__ uint32_t tap_addr(const Walk &wk, int a)
 {
-    const uint32_t al = row_addr(wn.lo, min(max(a, 0), h), pitch4);
-    const uint32_t ah = al + wn.dhi;
-    const float l0 = lds<0>(al), l1 = lds<4>(al), l2 = lds<8>(al), l3 = lds<12>(al), l4 = lds<16>(al);
-    const float h0 = lds<0>(ah), h1 = lds<4>(ah), h2 = lds<8>(ah), h3 = lds<12>(ah), h4 = lds<16>(ah);
-    TapRow o;
-    o.d[0] = cw.wh * h0 + cw.fh * h1 - cw.wl * l1 - cw.fl * l0;
-    o.d[1] = cw.wh * h1 + cw.fh * h2 - cw.wl * l2 - cw.fl * l1;
-    o.d[2] = cw.wh * h2 + cw.fh * h3 - cw.wl * l3 - cw.fl * l2;
-    o.d[3] = cw.wh * h3 + cw.fh * h4 - cw.wl * l4 - cw.fl * l3;
-    return o;
+    a = min(max(a, 0), wk.h);
+    return wk.lo + (uint32_t)(a * wk.pitch4) + (uint32_t)((a >> 3) << 2);
 }
 
-__device__ __forceinline__ TapRowE load_tap_row_e(const Windows &wn, int a, int h, int pitch4, const ColW &cw)
+struct ColW2 {        // column weights of a box, each broadcast to both halves
+    f2_t wh, fh, nwl, nfl, fl;
+};
+
+__device__ __forceinline__ ColW2 col_weights(const BoxTaps &t)
 {
-    const uint32_t al = row_addr(wn.lo, min(max(a, 0), h), pitch4);
-    const uint32_t ah = al + wn.dhi;
-    const float l0 = lds<0>(al), l1 = lds<4>(al), l2 = lds<8>(al), l3 = lds<12>(al), l4 = lds<16>(al);
-    const float h0 = lds<0>(ah), h1 = lds<4>(ah), h2 = lds<8>(ah), h3 = lds<12>(ah), h4 = lds<16>(ah);
-    TapRowE o;
-    o.e_lo[0] = l1 - l0; o.e_lo[1] = l2 - l1; o.e_lo[2] = l3 - l2; o.e_lo[3] = l4 - l3;
-    o.e_hi[0] = h1 - h0; o.e_hi[1] = h2 - h1; o.e_hi[2] = h3 - h2; o.e_hi[3] = h4 - h3;
-    // d = (1-f_hi) h[m] + f_hi h[m+1] - (1-f_lo) l[m+1] - f_lo l[m]
-    //   = (h[m] - l[m+1]) + f_hi e_hi[m] + f_lo e_lo[m]
-    o.d[0] = (h0 - l1) + cw.fh * o.e_hi[0] + cw.fl * o.e_lo[0];
-    o.d[1] = (h1 - l2) + cw.fh * o.e_hi[1] + cw.fl * o.e_lo[1];
-    o.d[2] = (h2 - l3) + cw.fh * o.e_hi[2] + cw.fl * o.e_lo[2];
-    o.d[3] = (h3 - l4) + cw.fh * o.e_hi[3] + cw.fl * o.e_lo[3];
-    return o;
+    ColW2 c;
+    c.wh = pack2(1.0f - t.f_hi_c, 1.0f - t.f_hi_c);
+    c.fh = pack2(t.f_hi_c, t.f_hi_c);
+    c.nwl = pack2(t.f_lo_c - 1.0f, t.f_lo_c - 1.0f);
+    c.nfl = pack2(-t.f_lo_c, -t.f_lo_c);
+    c.fl = pack2(t.f_lo_c, t.f_lo_c);
+    return c;
+}
+
+// Column-combined values d[m] of the tap rows a_lo (low halves) and a_hi (high halves):
+//   d = (1-f_hi) h[m] + f_hi h[m+1] - (1-f_lo) l[m+1] - f_lo l[m]
+__device__ __forceinline__ void load_pair(const Walk &wk, int a_lo, int a_hi, const ColW2 &cw, f2_t d[kStrip])
+{
+    const uint32_t al0 = tap_addr(wk, a_lo), ah0 = al0 + wk.dhi;
+    const uint32_t al1 = tap_addr(wk, a_hi), ah1 = al1 + wk.dhi;
+    const f2_t l0 = pack2(lds<0>(al0), lds<0>(al1)), l1 = pack2(lds<4>(al0), lds<4>(al1));
+    const f2_t l2 = pack2(lds<8>(al0), lds<8>(al1)), l3 = pack2(lds<12>(al0), lds<12>(al1));
+    const f2_t l4 = pack2(lds<16>(al0), lds<16>(al1));
+    const f2_t h0 = pack2(lds<0>(ah0), lds<0>(ah1)), h1 = pack2(lds<4>(ah0), lds<4>(ah1));
+    const f2_t h2 = pack2(lds<8>(ah0), lds<8>(ah1)), h3 = pack2(lds<12>(ah0), lds<12>(ah1));
+    const f2_t h4 = pack2(lds<16>(ah0), lds<16>(ah1));
+    d[0] = fma2(cw.nfl, l0, fma2(cw.nwl, l1, fma2(cw.fh, h1, mul2(cw.wh, h0))));
+    d[1] = fma2(cw.nfl, l1, fma2(cw.nwl, l2, fma2(cw.fh, h2, mul2(cw.wh, h1))));
+    d[2] = fma2(cw.nfl, l2, fma2(cw.nwl, l3, fma2(cw.fh, h3, mul2(cw.wh, h2))));
+    d[3] = fma2(cw.nfl, l3, fma2(cw.nwl, l4, fma2(cw.fh, h4, mul2(cw.wh, h3))));
+}
+
+// Same plus the one-column strips outside the box: e_lo[m] = l[m+1]-l[m], e_hi[m] = h[m+1]-h[m],
+// and d = (h[m] - l[m+1]) + f_hi e_hi[m] + f_lo e_lo[m].
+__device__ __forceinline__ void load_pair_e(const Walk &wk, int a_lo, int a_hi, const ColW2 &cw, f2_t d[kStrip],
+                                            f2_t el[kStrip], f2_t eh[kStrip])
+{
+    const uint32_t al0 = tap_addr(wk, a_lo), ah0 = al0 + wk.dhi;
+    const uint32_t al1 = tap_addr(wk, a_hi), ah1 = al1 + wk.dhi;
+    f2_t l[kStrip + 1], hh[kStrip + 1];
+    l[0] = pack2(lds<0>(al0), lds<0>(al1)); l[1] = pack2(lds<4>(al0), lds<4>(al1));
+    l[2] = pack2(lds<8>(al0), lds<8>(al1)); l[3] = pack2(lds<12>(al0), lds<12>(al1));
+    l[4] = pack2(lds<16>(al0), lds<16>(al1));
+    hh[0] = pack2(lds<0>(ah0), lds<0>(ah1)); hh[1] = pack2(lds<4>(ah0), lds<4>(ah1));
+    hh[2] = pack2(lds<8>(ah0), lds<8>(ah1)); hh[3] = pack2(lds<12>(ah0), lds<12>(ah1));
+    hh[4] = pack2(lds<16>(ah0), lds<16>(ah1));
+#pragma unroll
+    for (int m = 0; m < kStrip; ++m) {
+        el[m] = sub2(l[m + 1], l[m]);
+        eh[m] = sub2(hh[m + 1], hh[m]);
+        d[m] = fma2(cw.fl, el[m], fma2(cw.fh, eh[m], sub2(hh[m], l[m + 1])));
+    }
 }
 
 template <int T, bool FAST>
@@ -331,6 +412,7 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
     float *sI = reinterpret_cast<float *>(smem4);
     __shared__ __align__(16) float sRow[kMaxTiles * kTile];
     __shared__ __align__(16) float sCol[kMaxTiles * kTile];
+    __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
 
     const int64_t nc = blockIdx.x / fsplit;
     const int part = blockIdx.x % fsplit;
@@ -339,6 +421,11 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
     const Geometry g = geometry(h, w);
     const uint32_t sI32 = smem_u32(sI);
 
+    if ((int)threadIdx.x < f_end - f_begin) {
+        const Box box = load_box(bp, c * F + f_begin + threadIdx.x);
+        store_taps(sTaps + threadIdx.x * kTapWords,
+                   taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
+    }
     init_integral_padding(sI, g);
     build_integral<T, FAST>(x + nc * (int64_t)h * w, sI32, sRow, sCol, g);
 
@@ -346,37 +433,44 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
     const int cg = lane & 7, rg = lane >> 3;
 
     for (int f = f_begin; f < f_end; ++f) {
-        const Box box = load_box(bp, c * F + f);
-        const BoxTaps t = taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact);
-        const ColW cw = {1.0f - t.f_hi_c, t.f_hi_c, 1.0f - t.f_lo_c, t.f_lo_c};
+        const BoxTaps t = load_taps(sTaps + (f - f_begin) * kTapWords);
+        const ColW2 cw = col_weights(t);
+        const float sfl = t.scale * t.f_lo_r, sfh = t.scale * t.f_hi_r;
         float *o = out + (nc * F + f) * (int64_t)h * w;
 #pragma unroll
         for (int k = 0; k < T; ++k) {
             const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
             if (!tp.active) continue;
-            const Windows wn = windows(sI32, t, tp.q0, w);
-            TapRow ra = load_tap_row(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
-            TapRow rc = load_tap_row(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
+            const Walk wk = make_walk(sI32, t, tp.q0, g);
+            f2_t prev[kStrip];                 // (d of row lo-1, d of row hi) of the current pixel row
+            load_pair(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, prev);
             float *dst = o + tp.p0 * w + tp.q0;
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
                 const int p = tp.p0 + i;
                 if (FAST || p < h) {
-                    const TapRow rb = load_tap_row(wn, p + t.lo_r, h, g.pitch4, cw);
-                    const TapRow rd = load_tap_row(wn, p + t.hi_r + 1, h, g.pitch4, cw);
+                    f2_t cur[kStrip];          // (d of row lo, d of row hi+1)
+                    load_pair(wk, p + t.lo_r, p + t.hi_r + 1, cw, cur);
                     float v[kStrip];
 #pragma unroll
-                    for (int m = 0; m < kStrip; ++m)
-                        v[m] = combine_rows(ra.d[m], rb.d[m], rc.d[m], rd.d[m], t.f_lo_r, t.f_hi_r) * t.scale;
+                    for (int m = 0; m < kStrip; ++m) {
+                        // (C - B) + f_hi (D - C) + f_lo (B - A), times scale
+                        float b, dd, a, cc, top, bot;
+                        unpack2(cur[m], b, dd);
+                        unpack2(prev[m], a, cc);
+                        unpack2(sub2(cur[m], prev[m]), top, bot);
+                        v[m] = (cc - b) * t.scale + sfh * bot + sfl * top;
+                        (void)a; (void)dd;
+                        prev[m] = cur[m];
+                    }
                     if (FAST) {
-                        *reinterpret_cast<float4 *>(dst + i * w) = make_float4(v[0], v[1], v[2], v[3]);
+                        *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
                     } else {
 #pragma unroll
                         for (int m = 0; m < kStrip; ++m)
-                            if (tp.q0 + m < w) dst[i * w + m] = v[m];
+                            if (tp.q0 + m < w) dst[m] = v[m];
                     }
-                    ra = rb;
-                    rc = rd;
+                    dst += w;
                 }
             }
         }
@@ -396,6 +490,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     float *sX = sI + layout_floats(h, w);                  // the input plane, pitch w
     __shared__ __align__(16) float sRow[kMaxTiles * kTile];
     __shared__ __align__(16) float sCol[kMaxTiles * kTile];
+    __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
     __shared__ float red[16][kNumSums];
 
     const int64_t nc = blockIdx.x;
@@ -406,6 +501,10 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     const uint32_t sI32 = smem_u32(sI), sX32 = smem_u32(sX);
     const int npix = h * w;
 
+    if (tid < F) {
+        const Box box = load_box(bp, c * F + tid);
+        store_taps(sTaps + tid * kTapWords, taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
+    }
     init_integral_padding(sI, g);
     if (NEED_PARAMS) {
         const float *xp = x + nc * (int64_t)npix;
@@ -441,72 +540,94 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
             }
         }
 
-        const Box box = load_box(bp, c * F + f);
-        const BoxTaps t = taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact);
-        const ColW cw = {1.0f - t.f_hi_c, t.f_hi_c, 1.0f - t.f_lo_c, t.f_lo_c};
-        ParamSums sums = {0.f, 0.f, 0.f, 0.f, 0.f};
+        const BoxTaps t = load_taps(sTaps + f * kTapWords);
+        const ColW2 cw = col_weights(t);
+        // accumulators of this filter: see ParamSums.  The strip sums are kept per tap-row pair and
+        // combined after the walk: sum x*(C-B) in *1, (sum x*(B-A), sum x*(D-C)) in *2.
+        float s_out = 0.f, left1 = 0.f, right1 = 0.f;
+        f2_t topbot2 = pack2(0.f, 0.f), left2 = pack2(0.f, 0.f), right2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int k = 0; k < T; ++k) {
             const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
             if (tp.active) {
-                const Windows wn = windows(sI32, t, tp.q0, w);
+                const Walk wk = make_walk(sI32, t, tp.q0, g);
                 if (NEED_PARAMS) {
-                    TapRowE ra = load_tap_row_e(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
-                    TapRowE rc = load_tap_row_e(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
-                    const uint32_t xa = sX32 + (tp.p0 * w + tp.q0) * 4;
+                    f2_t pd[kStrip], pel[kStrip], peh[kStrip];
+                    load_pair_e(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, pd, pel, peh);
+                    uint32_t xa = sX32 + (tp.p0 * w + tp.q0) * 4;
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
                         const int p = tp.p0 + i;
                         if (FAST || p < h) {
-                            const TapRowE rb = load_tap_row_e(wn, p + t.lo_r, h, g.pitch4, cw);
-                            const TapRowE rd = load_tap_row_e(wn, p + t.hi_r + 1, h, g.pitch4, cw);
+                            f2_t cd[kStrip], cel[kStrip], ceh[kStrip];
+                            load_pair_e(wk, p + t.lo_r, p + t.hi_r + 1, cw, cd, cel, ceh);
                             float xv[kStrip];
                             if (FAST) {
-                                const float4 v = lds128(xa + i * w * 4);
+                                const float4 v = lds128(xa);
                                 xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
                             } else {
 #pragma unroll
                                 for (int m = 0; m < kStrip; ++m) xv[m] = tp.q0 + m < w ? sX[p * w + tp.q0 + m] : 0.0f;
                             }
+                            xa += w * 4;
 #pragma unroll
                             for (int m = 0; m < kStrip; ++m) {
-                                const float top = rb.d[m] - ra.d[m];
-                                const float bot = rd.d[m] - rc.d[m];
-                                const float gg = (rc.d[m] - rb.d[m]) + t.f_hi_r * bot + t.f_lo_r * top;
-                                const float sl = combine_rows(ra.e_lo[m], rb.e_lo[m], rc.e_lo[m], rd.e_lo[m], t.f_lo_r, t.f_hi_r);
-                                const float sr = combine_rows(ra.e_hi[m], rb.e_hi[m], rc.e_hi[m], rd.e_hi[m], t.f_lo_r, t.f_hi_r);
-                                sums.s_out += xv[m] * gg;
-                                sums.s_top += xv[m] * top;
-                                sums.s_bot += xv[m] * bot;
-                                sums.s_left += xv[m] * sl;
-                                sums.s_right += xv[m] * sr;
+                                const f2_t xx = pack2(xv[m], xv[m]);
+                                float lo_new, hi_new, lo_old, hi_old, top, bot;
+                                // d: gather value and the two row strips
+                                const f2_t dd = sub2(cd[m], pd[m]);
+                                unpack2(cd[m], lo_new, hi_new);
+                                unpack2(pd[m], lo_old, hi_old);
+                                unpack2(dd, top, bot);
+                                const float gg = (hi_old - lo_new) + t.f_hi_r * bot + t.f_lo_r * top;
+                                topbot2 = fma2(xx, dd, topbot2);
+                                s_out += xv[m] * gg;
                                 gin[k][i][m] += gg * t.scale;
+                                // e_lo / e_hi: the two column strips
+                                unpack2(cel[m], lo_new, hi_new);
+                                unpack2(pel[m], lo_old, hi_old);
+                                left2 = fma2(xx, sub2(cel[m], pel[m]), left2);
+                                left1 += xv[m] * (hi_old - lo_new);
+                                unpack2(ceh[m], lo_new, hi_new);
+                                unpack2(peh[m], lo_old, hi_old);
+                                right2 = fma2(xx, sub2(ceh[m], peh[m]), right2);
+                                right1 += xv[m] * (hi_old - lo_new);
+                                pd[m] = cd[m]; pel[m] = cel[m]; peh[m] = ceh[m];
                             }
-                            ra = rb;
-                            rc = rd;
                         }
                     }
                 } else {
-                    TapRow ra = load_tap_row(wn, tp.p0 + t.lo_r - 1, h, g.pitch4, cw);
-                    TapRow rc = load_tap_row(wn, tp.p0 + t.hi_r, h, g.pitch4, cw);
+                    f2_t prev[kStrip];
+                    load_pair(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, prev);
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
                         const int p = tp.p0 + i;
                         if (FAST || p < h) {
-                            const TapRow rb = load_tap_row(wn, p + t.lo_r, h, g.pitch4, cw);
-                            const TapRow rd = load_tap_row(wn, p + t.hi_r + 1, h, g.pitch4, cw);
+                            f2_t cur[kStrip];
+                            load_pair(wk, p + t.lo_r, p + t.hi_r + 1, cw, cur);
 #pragma unroll
-                            for (int m = 0; m < kStrip; ++m)
-                                gin[k][i][m] += combine_rows(ra.d[m], rb.d[m], rc.d[m], rd.d[m], t.f_lo_r, t.f_hi_r) * t.scale;
-                            ra = rb;
-                            rc = rd;
+                            for (int m = 0; m < kStrip; ++m) {
+                                float b, dd, a, cc, top, bot;
+                                unpack2(cur[m], b, dd);
+                                unpack2(prev[m], a, cc);
+                                unpack2(sub2(cur[m], prev[m]), top, bot);
+                                gin[k][i][m] += ((cc - b) + t.f_hi_r * bot + t.f_lo_r * top) * t.scale;
+                                (void)a; (void)dd;
+                                prev[m] = cur[m];
+                            }
                         }
                     }
                 }
             }
         }
         if (NEED_PARAMS) {
-            float v[kNumSums] = {sums.s_out, sums.s_top, sums.s_bot, sums.s_left, sums.s_right};
+            float tb_top, tb_bot, l_lo, l_hi, r_lo, r_hi;
+            unpack2(topbot2, tb_top, tb_bot);
+            unpack2(left2, l_lo, l_hi);
+            unpack2(right2, r_lo, r_hi);
+            float v[kNumSums] = {s_out, tb_top, tb_bot,
+                                 left1 + t.f_lo_r * l_lo + t.f_hi_r * l_hi,
+                                 right1 + t.f_lo_r * r_lo + t.f_hi_r * r_hi};
 #pragma unroll
             for (int j = 0; j < kNumSums; ++j) v[j] = warp_sum(v[j]);
             if (lane == 0) {
@@ -548,7 +669,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
 template <class K>
 int opt_in_smem(K kernel, size_t bytes)
 {
-    if (bytes <= 36 * 1024) return BC_OK;     // static scratch included, this stays under the 48 KB default
+    if (bytes <= 34 * 1024) return BC_OK;     // static scratch included, this stays under the 48 KB default
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
         return check_launch("shared memory opt-in");
     return BC_OK;
@@ -558,15 +679,16 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
-bool plane_path_fits_forward(int h, int w)
+bool plane_path_fits_forward(int F, int h, int w)
 {
-    return (size_t)layout_floats(h, w) * sizeof(float) <= kMaxSmem && warp_tiles(h, w) <= kMaxTiles;
+    return F <= kMaxFilters && (size_t)layout_floats(h, w) * sizeof(float) <= kMaxSmem &&
+           warp_tiles(h, w) <= kMaxTiles;
 }
 
-bool plane_path_fits_backward(int h, int w)
+bool plane_path_fits_backward(int F, int h, int w)
 {
     const size_t bytes = ((size_t)layout_floats(h, w) + (size_t)h * w) * sizeof(float);
-    return bytes <= kMaxSmem && warp_tiles(h, w) <= kMaxTiles;
+    return F <= kMaxFilters && bytes <= kMaxSmem && warp_tiles(h, w) <= kMaxTiles;
 }
 
 int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,

@@ -167,7 +167,7 @@ int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, i
 size_t bc_boxconv2d_forward_workspace(int N, int C, int F, int h, int w)
 {
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w)) return 0;
-    if (plane_path_fits_forward(h, w)) return 0;
+    if (plane_path_fits_forward(F, h, w)) return 0;
     return integral_bytes((int64_t)N * C, h, w);
 }
 
@@ -181,7 +181,7 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
     if (any_empty(N, C, F, h, w)) return BC_OK;
     if (!input || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
     const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
-    if (plane_path_fits_forward(h, w))
+    if (plane_path_fits_forward(F, h, w))
         return launch_forward_plane(input, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
         workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
@@ -195,7 +195,7 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
 size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
 {
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
-    if (plane_path_fits_backward(h, w))
+    if (plane_path_fits_backward(F, h, w))
         return align_up((size_t)C * F * N * kNumSums * sizeof(float), 256);
     return bc_box_convolution_backward_workspace(N, C, F, h, w, need_mask);
 }
@@ -229,7 +229,7 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
         workspace_bytes < bc_boxconv2d_backward_workspace(N, C, F, h, w, need_mask))
         return BC_ERR_WORKSPACE;
-    if (plane_path_fits_backward(h, w))
+    if (plane_path_fits_backward(F, h, w))
         return launch_backward_plane(input, grad_output, bp, reparametrization_h, reparametrization_w, N, C,
                                      F, h, w, normalize != 0, exact != 0, need_mask, grad_input,
                                      grad_params, static_cast<float *>(workspace), stream);
