@@ -33,6 +33,7 @@ SIGNATURES = {
     "bc_boxconv2d_backward_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_backward": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_launch_count": (ctypes.c_uint64, []),
+    "bc_wait_timeouts": (_i, [ctypes.POINTER(_i)]),
     "bc_profile_start": (_i, [_i]),
     "bc_profile_stop": (_i, []),
     "bc_profile_count": (_i, []),
@@ -54,3 +55,10 @@ def check(status, what):
         msg = lib.bc_status_string(status).decode()
         detail = lib.bc_last_cuda_error().decode()
         raise RuntimeError("%s failed: %s%s" % (what, msg, (" (" + detail + ")") if detail and status == -4 else ""))
+
+
+def wait_timeouts():
+    """Bounded waits that expired inside kernels on the current device (synchronises; 0 is healthy)."""
+    n = ctypes.c_int(0)
+    check(lib.bc_wait_timeouts(ctypes.byref(n)), "bc_wait_timeouts")
+    return n.value

@@ -77,6 +77,8 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
                           int need_mask, float *grad_input, float *grad_params, float *partials,
                           cudaStream_t s);
 
+int read_wait_timeouts(int *count);
+
 int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int count, double rep_h,
                 double rep_w, double max_h, double max_w, bool exact, cudaStream_t s);
 

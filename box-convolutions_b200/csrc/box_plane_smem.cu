@@ -128,26 +128,32 @@ __device__ __forceinline__ Geometry geometry(int h, int w)
     return g;
 }
 
-struct TilePos {
+// Everything a thread needs to know about one of its strips; computed once per kernel.
+struct Strip {
     int p0, q0, rt, ct;
+    int pix;              // p0*w + q0: offset of the strip's first pixel in a plane
+    uint32_t store;       // shared address of column q0 of integral row p0+1
     bool tile;            // the warp tile exists
-    bool active;          // ... and this thread's strip has pixels inside the plane
+    bool active;          // ... and this strip has pixels inside the plane
 };
 
-__device__ __forceinline__ TilePos tile_pos(const Geometry &g, int wt, int cg, int rg)
+__device__ __forceinline__ Strip make_strip(const Geometry &g, uint32_t sI32, int wt, int cg, int rg)
 {
-    TilePos t;
+    Strip t;
     t.rt = wt / g.col_tiles;
     t.ct = wt - t.rt * g.col_tiles;
     t.p0 = t.rt * kTile + rg * kR;
     t.q0 = t.ct * kTile + cg * kStrip;
+    t.pix = t.p0 * g.w + t.q0;
     t.tile = wt < g.ntiles;
     t.active = t.tile && t.p0 < g.h && t.q0 < g.w;
+    const int a = t.p0 + 1;
+    t.store = sI32 + (kPad + t.q0) * 4 + a * g.pitch4 + ((a >> 3) << 2);
     return t;
 }
 
 // Zeroes what never changes in the integral image: row 0 and the left-hand padding (and column
-// 0) of every row.  Followed by the barriers inside build_integral().
+// 0) of every row.  Followed by the barriers inside the build.
 __device__ __forceinline__ void init_integral_padding(float *sI, const Geometry &g)
 {
     const int pitch = g.pitch4 >> 2;
@@ -158,128 +164,157 @@ __device__ __forceinline__ void init_integral_padding(float *sI, const Geometry 
     }
 }
 
-// Builds the integral image of one h x w plane (global memory) in shared memory: rows 1..h,
-// columns 1..w and the right-hand padding (init_integral_padding() provides the rest).
-// sRow / sCol: scratch for the totals exchanged between warps (kMaxTiles*32 floats each).
-// All threads of the CTA must call it; it ends with a barrier.
-template <int T, bool FAST>
-__device__ __forceinline__ void build_integral(const float *__restrict__ src, uint32_t sI32, float *sRow,
-                                               float *sCol, const Geometry &g)
+// ---- asynchronous bulk copies (TMA, no tensor map) global -> shared, completion on an mbarrier.
+// Every wait is bounded: when the limit expires the kernel counts the event in g_wait_timeouts
+// and carries on, so a lost copy shows up as a reported error instead of a hung GPU.
+__device__ int g_wait_timeouts = 0;
+constexpr long long kWaitLimitCycles = 2000000000LL;      // about a second
+
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count)
 {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int cg = lane & 7, rg = lane >> 3;
-    const int h = g.h, w = g.w;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t mbar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity)
+{
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                     " selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(mbar), "r"(parity), "r"(2000u) : "memory");
+        if (done) return true;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
+    }
+}
 
+// Register block of a strip while the integral image is being built.
+template <int T>
+struct Blocks {
     float v[T][kR][kStrip];
-    TilePos tp[T];
+    float carry[T][kR];
+};
 
-    // ---- load
+// Build, part 1: fetch every strip's 8 x 4 block (from the staged copy of the plane in shared
+// memory when STAGED, else from global memory), prefix it along rows inside the thread and across
+// the 8 column-group lanes, publish the tile's row totals.  Ends with a barrier, after which the
+// staged plane is no longer needed.
+template <int T, bool FAST, bool STAGED>
+__device__ __forceinline__ void build_rows(Blocks<T> &b, const Strip (&st)[T], const float *__restrict__ src,
+                                           uint32_t sG32, float *sRow, const Geometry &g, int cg, int rg)
+{
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        tp[k] = tile_pos(g, warp + k * nwarps, cg, rg);
-        const float *s = src + tp[k].p0 * w + tp[k].q0;
 #pragma unroll
         for (int i = 0; i < kR; ++i) {
-            if (FAST) {
-                const float4 t = tp[k].active ? __ldg(reinterpret_cast<const float4 *>(s + i * w))
+            if (STAGED) {
+                const float4 t = st[k].active ? lds128(sG32 + (st[k].pix + i * g.w) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                b.v[k][i][0] = t.x; b.v[k][i][1] = t.y; b.v[k][i][2] = t.z; b.v[k][i][3] = t.w;
+            } else if (FAST) {
+                const float4 t = st[k].active ? __ldg(reinterpret_cast<const float4 *>(src + st[k].pix + i * g.w))
                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-                v[k][i][0] = t.x; v[k][i][1] = t.y; v[k][i][2] = t.z; v[k][i][3] = t.w;
+                b.v[k][i][0] = t.x; b.v[k][i][1] = t.y; b.v[k][i][2] = t.z; b.v[k][i][3] = t.w;
             } else {
-                const bool in = tp[k].active && tp[k].p0 + i < h;
+                const bool in = st[k].active && st[k].p0 + i < g.h;
 #pragma unroll
                 for (int m = 0; m < kStrip; ++m)
-                    v[k][i][m] = (in && tp[k].q0 + m < w) ? __ldg(s + i * w + m) : 0.0f;
+                    b.v[k][i][m] = (in && st[k].q0 + m < g.w) ? __ldg(src + st[k].pix + i * g.w + m) : 0.0f;
             }
         }
     }
-
-    // ---- along rows: in-thread, across the 8 column-group lanes, across the warps of a tile row
-    float carry[T][kR];
 #pragma unroll
     for (int k = 0; k < T; ++k) {
+        float tot[kR];
 #pragma unroll
         for (int i = 0; i < kR; ++i) {
-            v[k][i][1] += v[k][i][0]; v[k][i][2] += v[k][i][1]; v[k][i][3] += v[k][i][2];
-            const float own = v[k][i][3];
+            b.v[k][i][1] += b.v[k][i][0]; b.v[k][i][2] += b.v[k][i][1]; b.v[k][i][3] += b.v[k][i][2];
+            const float own = b.v[k][i][3];
             float incl = own;
 #pragma unroll
             for (int d = 1; d < 8; d <<= 1) {
                 const float u = __shfl_up_sync(0xffffffffu, incl, d, 8);
-                if (cg >= d) incl += u;
+                incl += cg >= d ? u : 0.0f;
             }
-            carry[k][i] = incl - own;
-            if (cg == 7 && tp[k].tile) sRow[(tp[k].ct * g.row_tiles + tp[k].rt) * kTile + rg * kR + i] = incl;
+            b.carry[k][i] = incl - own;
+            tot[i] = incl;
+        }
+        if (cg == 7 && st[k].tile) {
+            float4 *dst = reinterpret_cast<float4 *>(sRow + (st[k].ct * g.row_tiles + st[k].rt) * kTile + rg * kR);
+            dst[0] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+            dst[1] = make_float4(tot[4], tot[5], tot[6], tot[7]);
         }
     }
     __syncthreads();
+}
+
+// Build, part 2: row totals of the tiles to the left, prefix down the columns (thread, the 4
+// row-group lanes, tiles above), store rows p0+1 .. p0+8 with the right-hand padding.  Ends with
+// a barrier: the integral image is complete.
+template <int T, bool FAST>
+__device__ __forceinline__ void build_columns(Blocks<T> &b, const Strip (&st)[T], float *sRow, float *sCol,
+                                              const Geometry &g, int cg, int rg)
+{
+    float ccarry[T][kStrip];
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        if (tp[k].tile) {
-            for (int c2 = 0; c2 < tp[k].ct; ++c2) {
-                const float4 *s = reinterpret_cast<const float4 *>(sRow + (c2 * g.row_tiles + tp[k].rt) * kTile + rg * kR);
-                const float4 a = s[0], b = s[1];
-                carry[k][0] += a.x; carry[k][1] += a.y; carry[k][2] += a.z; carry[k][3] += a.w;
-                carry[k][4] += b.x; carry[k][5] += b.y; carry[k][6] += b.z; carry[k][7] += b.w;
+        if (st[k].tile) {
+            for (int c2 = 0; c2 < st[k].ct; ++c2) {
+                const float4 *s = reinterpret_cast<const float4 *>(sRow + (c2 * g.row_tiles + st[k].rt) * kTile + rg * kR);
+                const float4 x = s[0], y = s[1];
+                b.carry[k][0] += x.x; b.carry[k][1] += x.y; b.carry[k][2] += x.z; b.carry[k][3] += x.w;
+                b.carry[k][4] += y.x; b.carry[k][5] += y.y; b.carry[k][6] += y.z; b.carry[k][7] += y.w;
             }
         }
         // apply the row carry and run the in-thread column prefix in the same sweep
 #pragma unroll
-        for (int m = 0; m < kStrip; ++m) v[k][0][m] += carry[k][0];
+        for (int m = 0; m < kStrip; ++m) b.v[k][0][m] += b.carry[k][0];
 #pragma unroll
         for (int i = 1; i < kR; ++i)
 #pragma unroll
-            for (int m = 0; m < kStrip; ++m) v[k][i][m] += carry[k][i] + v[k][i - 1][m];
-    }
+            for (int m = 0; m < kStrip; ++m) b.v[k][i][m] += b.carry[k][i] + b.v[k][i - 1][m];
 
-    // ---- down columns: across the 4 row-group lanes, across the warps of a tile column
-    float ccarry[T][kStrip];
-#pragma unroll
-    for (int k = 0; k < T; ++k) {
         float tot[kStrip];
 #pragma unroll
         for (int m = 0; m < kStrip; ++m) {
-            const float own = v[k][kR - 1][m];
+            const float own = b.v[k][kR - 1][m];
             float incl = own;
             float u = __shfl_up_sync(0xffffffffu, incl, 8);
-            if (rg >= 1) incl += u;
+            incl += rg >= 1 ? u : 0.0f;
             u = __shfl_up_sync(0xffffffffu, incl, 16);
-            if (rg >= 2) incl += u;
+            incl += rg >= 2 ? u : 0.0f;
             ccarry[k][m] = incl - own;
             tot[m] = incl;
         }
-        if (rg == 3 && tp[k].tile)
-            *reinterpret_cast<float4 *>(sCol + (tp[k].rt * g.col_tiles + tp[k].ct) * kTile + cg * kStrip) =
+        if (rg == 3 && st[k].tile)
+            *reinterpret_cast<float4 *>(sCol + (st[k].rt * g.col_tiles + st[k].ct) * kTile + cg * kStrip) =
                 make_float4(tot[0], tot[1], tot[2], tot[3]);
     }
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < T; ++k) {
-        if (tp[k].tile) {
-            for (int r2 = 0; r2 < tp[k].rt; ++r2) {
-                const float4 a = *reinterpret_cast<const float4 *>(sCol + (r2 * g.col_tiles + tp[k].ct) * kTile + cg * kStrip);
-                ccarry[k][0] += a.x; ccarry[k][1] += a.y; ccarry[k][2] += a.z; ccarry[k][3] += a.w;
+        if (st[k].tile) {
+            for (int r2 = 0; r2 < st[k].rt; ++r2) {
+                const float4 x = *reinterpret_cast<const float4 *>(sCol + (r2 * g.col_tiles + st[k].ct) * kTile + cg * kStrip);
+                ccarry[k][0] += x.x; ccarry[k][1] += x.y; ccarry[k][2] += x.z; ccarry[k][3] += x.w;
             }
         }
-    }
-
-    // ---- store rows p0+1 .. p0+8, columns q0+1 .. q0+4, and the right-hand padding
-#pragma unroll
-    for (int k = 0; k < T; ++k) {
-        if (tp[k].active) {
-            const int q0 = tp[k].q0;
-            // address of column q0 of row a; the +1 column shift is in the immediates
-            const uint32_t col = sI32 + (kPad + q0) * 4;
-            const bool last = q0 + kStrip >= w;
-            const int npad = w - q0;     // padding columns this strip still has to fill (1..4) when `last`
-            const uint32_t ra0 = row_addr(col, tp[k].p0 + 1, g.pitch4);
+        if (st[k].active) {
+            const bool last = st[k].q0 + kStrip >= g.w;
+            const int npad = g.w - st[k].q0;      // padding columns still to fill (1..4) when `last`
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
-                const int a = tp[k].p0 + i + 1;
-                if (FAST || a <= h) {
+                if (FAST || st[k].p0 + i < g.h) {
                     // p0 is a multiple of 8, so only the last of the 8 rows moves to the next skew
-                    const uint32_t ra = ra0 + i * g.pitch4 + (i == kR - 1 ? 4 : 0);
-                    const float x0 = v[k][i][0] + ccarry[k][0], x1 = v[k][i][1] + ccarry[k][1];
-                    const float x2 = v[k][i][2] + ccarry[k][2], x3 = v[k][i][3] + ccarry[k][3];
+                    const uint32_t ra = st[k].store + i * g.pitch4 + (i == kR - 1 ? 4 : 0);
+                    const float x0 = b.v[k][i][0] + ccarry[k][0], x1 = b.v[k][i][1] + ccarry[k][1];
+                    const float x2 = b.v[k][i][2] + ccarry[k][2], x3 = b.v[k][i][3] + ccarry[k][3];
                     // past the plane's last column the running value is I[a][w], which is exactly
                     // what the right-hand padding has to hold
                     sts<4>(ra, x0); sts<8>(ra, x1); sts<12>(ra, x2); sts<16>(ra, x3);
@@ -404,22 +439,28 @@ __device__ __forceinline__ void load_pair_e(const Walk &wk, int a_lo, int a_hi, 
 }
 
 template <int T, bool FAST>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, T == 1 ? 4 : 1)
 forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restrict__ out, int C, int F,
                      int h, int w, int fsplit, bool normalize, bool exact)
 {
     extern __shared__ float4 smem4[];
     float *sI = reinterpret_cast<float *>(smem4);
-    __shared__ __align__(16) float sRow[kMaxTiles * kTile];
-    __shared__ __align__(16) float sCol[kMaxTiles * kTile];
+    const Geometry g = geometry(h, w);
+    float *sRow = sI + layout_floats(h, w);
+    float *sCol = sRow + g.ntiles * kTile;
     __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
 
     const int64_t nc = blockIdx.x / fsplit;
     const int part = blockIdx.x % fsplit;
     const int c = (int)(nc % C);
     const int f_begin = (F * part) / fsplit, f_end = (F * (part + 1)) / fsplit;
-    const Geometry g = geometry(h, w);
     const uint32_t sI32 = smem_u32(sI);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int cg = lane & 7, rg = lane >> 3;
+
+    Strip st[T];
+#pragma unroll
+    for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
 
     if ((int)threadIdx.x < f_end - f_begin) {
         const Box box = load_box(bp, c * F + f_begin + threadIdx.x);
@@ -427,10 +468,11 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
                    taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
     }
     init_integral_padding(sI, g);
-    build_integral<T, FAST>(x + nc * (int64_t)h * w, sI32, sRow, sCol, g);
-
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int cg = lane & 7, rg = lane >> 3;
+    {
+        Blocks<T> blk;
+        build_rows<T, FAST, false>(blk, st, x + nc * (int64_t)h * w, 0u, sRow, g, cg, rg);
+        build_columns<T, FAST>(blk, st, sRow, sCol, g, cg, rg);
+    }
 
     for (int f = f_begin; f < f_end; ++f) {
         const BoxTaps t = load_taps(sTaps + (f - f_begin) * kTapWords);
@@ -439,15 +481,14 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
         float *o = out + (nc * F + f) * (int64_t)h * w;
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
-            if (!tp.active) continue;
-            const Walk wk = make_walk(sI32, t, tp.q0, g);
+            if (!st[k].active) continue;
+            const Walk wk = make_walk(sI32, t, st[k].q0, g);
             f2_t prev[kStrip];                 // (d of row lo-1, d of row hi) of the current pixel row
-            load_pair(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, prev);
-            float *dst = o + tp.p0 * w + tp.q0;
+            load_pair(wk, st[k].p0 + t.lo_r - 1, st[k].p0 + t.hi_r, cw, prev);
+            float *dst = o + st[k].pix;
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
-                const int p = tp.p0 + i;
+                const int p = st[k].p0 + i;
                 if (FAST || p < h) {
                     f2_t cur[kStrip];          // (d of row lo, d of row hi+1)
                     load_pair(wk, p + t.lo_r, p + t.hi_r + 1, cw, cur);
@@ -468,7 +509,7 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
                     } else {
 #pragma unroll
                         for (int m = 0; m < kStrip; ++m)
-                            if (tp.q0 + m < w) dst[m] = v[m];
+                            if (st[k].q0 + m < w) dst[m] = v[m];
                     }
                     dst += w;
                 }
@@ -479,34 +520,58 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
 
 // T = warp tiles per warp: grad-input accumulators are registers, so the number of strips a
 // thread owns is a compile-time constant.
-template <int T, bool FAST, bool NEED_PARAMS>
+// STAGED: the input plane and each grad_output plane arrive in shared memory by asynchronous bulk
+// copies (one instruction per plane, issued by one thread); the copy of the next grad_output
+// plane runs while the current one is gathered.
+template <int T, bool FAST, bool STAGED, bool NEED_PARAMS>
 __global__ void __launch_bounds__(512)
 backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ grad_output, BoxParams bp,
                       float *__restrict__ grad_input, float *__restrict__ partials, int N, int C, int F,
                       int h, int w, bool normalize, bool exact, bool write_gin)
 {
     extern __shared__ float4 smem4[];
+    const Geometry g = geometry(h, w);
+    const int npix = h * w;
     float *sI = reinterpret_cast<float *>(smem4);          // integral(grad_output plane)
-    float *sX = sI + layout_floats(h, w);                  // the input plane, pitch w
-    __shared__ __align__(16) float sRow[kMaxTiles * kTile];
-    __shared__ __align__(16) float sCol[kMaxTiles * kTile];
+    float *sRow = sI + layout_floats(h, w);
+    float *sCol = sRow + g.ntiles * kTile;
+    float *sX = sCol + g.ntiles * kTile;                   // the input plane, pitch w (NEED_PARAMS)
+    float *sG = sX + (NEED_PARAMS ? npix : 0);             // staged grad_output plane (STAGED)
     __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
     __shared__ float red[16][kNumSums];
+    __shared__ __align__(8) unsigned long long mbar[2];
 
     const int64_t nc = blockIdx.x;
     const int c = (int)(nc % C), n = (int)(nc / C);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int cg = lane & 7, rg = lane >> 3;
-    const Geometry g = geometry(h, w);
-    const uint32_t sI32 = smem_u32(sI), sX32 = smem_u32(sX);
-    const int npix = h * w;
+    const uint32_t sI32 = smem_u32(sI), sX32 = smem_u32(sX), sG32 = smem_u32(sG);
+    const uint32_t mbarX = smem_u32(&mbar[0]), mbarG = smem_u32(&mbar[1]);
+    const float *gbase = grad_output + nc * F * (int64_t)npix;
+    const uint32_t plane_bytes = (uint32_t)npix * 4u;
+    bool timed_out = false;
 
+    Strip st[T];
+#pragma unroll
+    for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
+
+    if (STAGED && tid == 0) {
+        mbar_init(mbarX, 1);
+        mbar_init(mbarG, 1);
+        fence_mbar_init();
+    }
     if (tid < F) {
         const Box box = load_box(bp, c * F + tid);
         store_taps(sTaps + tid * kTapWords, taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
     }
     init_integral_padding(sI, g);
-    if (NEED_PARAMS) {
+    if (STAGED) {
+        __syncthreads();                                   // barriers initialised before anyone waits
+        if (tid == 0) {
+            bulk_load(sG32, gbase, plane_bytes, mbarG);
+            if (NEED_PARAMS) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
+        }
+    } else if (NEED_PARAMS) {
         const float *xp = x + nc * (int64_t)npix;
         if (FAST) {
             for (int i = tid; i < (npix >> 2); i += blockDim.x)
@@ -526,19 +591,27 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
 
     for (int f = 0; f < F; ++f) {
         // (the barrier that ends the previous iteration protects sI, sRow, sCol)
-        const float *gplane = grad_output + (nc * F + f) * (int64_t)npix;
-        build_integral<T, FAST>(gplane, sI32, sRow, sCol, g);
-        if (f + 1 < F && cg == 0) {
+        {
+            Blocks<T> blk;
+            if (STAGED) timed_out |= !mbar_wait(mbarG, f & 1);
+            build_rows<T, FAST, STAGED>(blk, st, gbase + f * (int64_t)npix, sG32, sRow, g, cg, rg);
+            if (STAGED && tid == 0 && f + 1 < F) {
+                // every thread has taken its block out of the staging buffer (barrier above)
+                fence_proxy_async();
+                bulk_load(sG32, gbase + (f + 1) * (int64_t)npix, plane_bytes, mbarG);
+            }
+            build_columns<T, FAST>(blk, st, sRow, sCol, g, cg, rg);
+        }
+        if (!STAGED && f + 1 < F && cg == 0) {
             // pull the next grad_output plane towards L2 while this one is gathered
 #pragma unroll
-            for (int k = 0; k < T; ++k) {
-                const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
+            for (int k = 0; k < T; ++k)
 #pragma unroll
                 for (int i = 0; i < kR; ++i)
-                    if (tp.active && tp.p0 + i < h)
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(gplane + npix + (tp.p0 + i) * w + tp.q0));
-            }
+                    if (st[k].active && st[k].p0 + i < h)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(gbase + (f + 1) * (int64_t)npix + st[k].pix + i * w));
         }
+        if (STAGED && NEED_PARAMS && f == 0) timed_out |= !mbar_wait(mbarX, 0);
 
         const BoxTaps t = load_taps(sTaps + f * kTapWords);
         const ColW2 cw = col_weights(t);
@@ -548,16 +621,15 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
         f2_t topbot2 = pack2(0.f, 0.f), left2 = pack2(0.f, 0.f), right2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
-            if (tp.active) {
-                const Walk wk = make_walk(sI32, t, tp.q0, g);
+            if (st[k].active) {
+                const Walk wk = make_walk(sI32, t, st[k].q0, g);
                 if (NEED_PARAMS) {
                     f2_t pd[kStrip], pel[kStrip], peh[kStrip];
-                    load_pair_e(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, pd, pel, peh);
-                    uint32_t xa = sX32 + (tp.p0 * w + tp.q0) * 4;
+                    load_pair_e(wk, st[k].p0 + t.lo_r - 1, st[k].p0 + t.hi_r, cw, pd, pel, peh);
+                    uint32_t xa = sX32 + st[k].pix * 4;
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
-                        const int p = tp.p0 + i;
+                        const int p = st[k].p0 + i;
                         if (FAST || p < h) {
                             f2_t cd[kStrip], cel[kStrip], ceh[kStrip];
                             load_pair_e(wk, p + t.lo_r, p + t.hi_r + 1, cw, cd, cel, ceh);
@@ -567,7 +639,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
                                 xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
                             } else {
 #pragma unroll
-                                for (int m = 0; m < kStrip; ++m) xv[m] = tp.q0 + m < w ? sX[p * w + tp.q0 + m] : 0.0f;
+                                for (int m = 0; m < kStrip; ++m) xv[m] = st[k].q0 + m < w ? sX[p * w + st[k].q0 + m] : 0.0f;
                             }
                             xa += w * 4;
 #pragma unroll
@@ -598,10 +670,10 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
                     }
                 } else {
                     f2_t prev[kStrip];
-                    load_pair(wk, tp.p0 + t.lo_r - 1, tp.p0 + t.hi_r, cw, prev);
+                    load_pair(wk, st[k].p0 + t.lo_r - 1, st[k].p0 + t.hi_r, cw, prev);
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
-                        const int p = tp.p0 + i;
+                        const int p = st[k].p0 + i;
                         if (FAST || p < h) {
                             f2_t cur[kStrip];
                             load_pair(wk, p + t.lo_r, p + t.hi_r + 1, cw, cur);
@@ -641,24 +713,24 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
             for (int j = 0; j < nwarps; ++j) s += red[j][tid];
             partials[((int64_t)(c * F + f) * N + n) * kNumSums + tid] = s;
         }
-        // red[] is next written after the barriers inside the next build_integral
+        // red[] is next written after the barriers inside the next build
     }
+    if (STAGED && timed_out && lane == 0) atomicAdd(&g_wait_timeouts, 1);
 
     if (write_gin) {
         float *gi = grad_input + nc * (int64_t)npix;
 #pragma unroll
         for (int k = 0; k < T; ++k) {
-            const TilePos tp = tile_pos(g, warp + k * nwarps, cg, rg);
-            if (tp.active) {
-                float *dst = gi + tp.p0 * w + tp.q0;
+            if (st[k].active) {
+                float *dst = gi + st[k].pix;
 #pragma unroll
                 for (int i = 0; i < kR; ++i) {
                     if (FAST) {
                         *reinterpret_cast<float4 *>(dst + i * w) = make_float4(gin[k][i][0], gin[k][i][1], gin[k][i][2], gin[k][i][3]);
-                    } else if (tp.p0 + i < h) {
+                    } else if (st[k].p0 + i < h) {
 #pragma unroll
                         for (int m = 0; m < kStrip; ++m)
-                            if (tp.q0 + m < w) dst[i * w + m] = gin[k][i][m];
+                            if (st[k].q0 + m < w) dst[i * w + m] = gin[k][i][m];
                     }
                 }
             }
@@ -679,16 +751,24 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
+size_t forward_smem_bytes(int h, int w)
+{
+    return ((size_t)layout_floats(h, w) + 2 * (size_t)warp_tiles(h, w) * kTile) * sizeof(float);
+}
+
+size_t backward_smem_bytes(int h, int w, bool need_params, bool staged)
+{
+    return forward_smem_bytes(h, w) + ((need_params ? (size_t)h * w : 0) + (staged ? (size_t)h * w : 0)) * sizeof(float);
+}
+
 bool plane_path_fits_forward(int F, int h, int w)
 {
-    return F <= kMaxFilters && (size_t)layout_floats(h, w) * sizeof(float) <= kMaxSmem &&
-           warp_tiles(h, w) <= kMaxTiles;
+    return F <= kMaxFilters && warp_tiles(h, w) <= kMaxTiles && forward_smem_bytes(h, w) <= kMaxSmem;
 }
 
 bool plane_path_fits_backward(int F, int h, int w)
 {
-    const size_t bytes = ((size_t)layout_floats(h, w) + (size_t)h * w) * sizeof(float);
-    return F <= kMaxFilters && bytes <= kMaxSmem && warp_tiles(h, w) <= kMaxTiles;
+    return F <= kMaxFilters && warp_tiles(h, w) <= kMaxTiles && backward_smem_bytes(h, w, true, false) <= kMaxSmem;
 }
 
 int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
@@ -700,7 +780,7 @@ int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N,
     int fsplit = 1;
     if (F % 2 == 0 && planes < 148 * 6) fsplit = 2;
     if (planes * fsplit > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
-    const size_t smem = (size_t)layout_floats(h, w) * sizeof(float);
+    const size_t smem = forward_smem_bytes(h, w);
     const int tiles = warp_tiles(h, w);
     const int T = tiles > 16 ? 4 : (tiles > 8 ? 2 : 1);
     const int warps = (tiles + T - 1) / T;
@@ -726,19 +806,27 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const bool need_params = (need_mask & (BC_NEED_ALL & ~BC_NEED_INPUT)) != 0;
     const bool write_gin = (need_mask & BC_NEED_INPUT) != 0;
-    const size_t smem = ((size_t)layout_floats(h, w) + (need_params ? (size_t)h * w : 0)) * sizeof(float);
     const int tiles = warp_tiles(h, w);
     const int T = tiles > 8 ? 2 : 1;
     const int warps = (tiles + T - 1) / T;
     const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(grad_output) &&
                       (!write_gin || aligned16(grad_input));
+    // bulk copies need 16-byte aligned planes of a multiple of 16 bytes (implied by `fast`) and room
+    // for the staging buffer; staging must not cost a resident CTA (two fit below ~112 KB each)
+    const size_t with_staging = backward_smem_bytes(h, w, need_params, true);
+    const size_t two_ctas = 112 * 1024;
+    const bool staged = fast && T == 1 && with_staging <= kMaxSmem &&
+                        (with_staging <= two_ctas || backward_smem_bytes(h, w, need_params, false) > two_ctas);
+    const size_t smem = backward_smem_bytes(h, w, need_params, staged);
     void (*kern)(const float *, const float *, BoxParams, float *, float *, int, int, int, int, int, bool, bool, bool);
-    if (fast) {
-        kern = T == 1 ? (need_params ? backward_plane_kernel<1, true, true> : backward_plane_kernel<1, true, false>)
-                      : (need_params ? backward_plane_kernel<2, true, true> : backward_plane_kernel<2, true, false>);
+    if (staged) {
+        kern = need_params ? backward_plane_kernel<1, true, true, true> : backward_plane_kernel<1, true, true, false>;
+    } else if (fast) {
+        kern = T == 1 ? (need_params ? backward_plane_kernel<1, true, false, true> : backward_plane_kernel<1, true, false, false>)
+                      : (need_params ? backward_plane_kernel<2, true, false, true> : backward_plane_kernel<2, true, false, false>);
     } else {
-        kern = T == 1 ? (need_params ? backward_plane_kernel<1, false, true> : backward_plane_kernel<1, false, false>)
-                      : (need_params ? backward_plane_kernel<2, false, true> : backward_plane_kernel<2, false, false>);
+        kern = T == 1 ? (need_params ? backward_plane_kernel<1, false, false, true> : backward_plane_kernel<1, false, false, false>)
+                      : (need_params ? backward_plane_kernel<2, false, false, true> : backward_plane_kernel<2, false, false, false>);
     }
     int st = opt_in_smem(kern, smem);
     if (st != BC_OK) return st;
@@ -751,6 +839,14 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     if (st != BC_OK || !need_params) return st;
     return launch_finish_param_grads(partials, bp, C * F, N, normalize, exact, rep_h, rep_w, need_mask,
                                      grad_params, s);
+}
+
+// Number of bounded waits that expired on the current device since the library was loaded
+// (synchronises).  Nonzero means an asynchronous copy never signalled completion.
+int read_wait_timeouts(int *count)
+{
+    if (cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(int)) != cudaSuccess) return check_launch("read_wait_timeouts");
+    return BC_OK;
 }
 
 }  // namespace bc

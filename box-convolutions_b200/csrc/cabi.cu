@@ -244,6 +244,12 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
 
 uint64_t bc_launch_count(void) { return g_launches.load(); }
 
+int bc_wait_timeouts(int *count)
+{
+    if (!count) return BC_ERR_NULL_POINTER;
+    return read_wait_timeouts(count);
+}
+
 int bc_profile_start(int capacity)
 {
     if (capacity < 0) return BC_ERR_BAD_SHAPE;

@@ -129,6 +129,10 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
  * bc_profile_get(i, ...) returns kernel id and milliseconds of record i;
  * bc_kernel_name(id) names the kernel. */
 uint64_t bc_launch_count(void);
+/* Kernels that stage planes with asynchronous bulk copies wait for them with a time limit
+ * (about a second); *count receives how many such waits have expired on the current device since
+ * the library was loaded.  Synchronises the device.  Anything but 0 means results are invalid. */
+int bc_wait_timeouts(int *count);
 int bc_profile_start(int capacity);
 int bc_profile_stop(void);
 int bc_profile_count(void);

@@ -289,3 +289,11 @@ def test_errors_are_loud(bc):
         bc.box_convolution_forward(integ, p, p, p, p, True, True)  # rows != channels
     with pytest.raises(RuntimeError):
         bc.BoxConv2d(2, 2, 8, 8)(torch.zeros(1, 2, 8, 8))          # module on CPU
+
+
+def test_no_bounded_wait_expired(bc):
+    """Runs last in this file: the asynchronous plane copies of the staged kernels all completed."""
+    from box_convolution import _cabi
+    wl = make_workload("cfg2", batch=2)
+    run_module(bc, wl.x, wl.stored, wl.grad_output, wl.max_h, wl.max_w, 8, True, True)
+    assert _cabi.wait_timeouts() == 0
