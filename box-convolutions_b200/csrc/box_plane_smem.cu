@@ -97,13 +97,6 @@ __device__ __forceinline__ f2_t sub2(f2_t a, f2_t b)
     return r;
 }
 
-// Byte address of column -kPad of row a, given the byte address of the image: rows are pitch4
-// bytes apart and row a is skewed by a/8 floats.
-__device__ __forceinline__ uint32_t row_addr(uint32_t base, int a, int pitch4)
-{
-    return base + a * pitch4 + ((a >> 1) & ~3);
-}
-
 inline int warp_tiles(int h, int w) { return ((w + kTile - 1) / kTile) * ((h + kTile - 1) / kTile); }
 
 __device__ __forceinline__ float warp_sum(float v)
