@@ -32,6 +32,7 @@ SIGNATURES = {
     "bc_boxconv2d_forward": (_i, [_vp] * 5 + [_f, _f, _vp] + [_i] * 7 + [_vp, _sz, _vp]),
     "bc_boxconv2d_backward_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_backward": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
+    "bc_boxconv2d_backward_static": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp]),
     "bc_launch_count": (ctypes.c_uint64, []),
     "bc_wait_timeouts": (_i, [ctypes.POINTER(_i)]),
     "bc_profile_start": (_i, [_i]),

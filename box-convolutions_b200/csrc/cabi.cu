@@ -242,6 +242,57 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                                   need_mask, grad_input, grad_params, partials, stream);
 }
 
+// ---- backward pass on the library's own scratch array (see the header for who needs this)
+static __device__ __align__(256) unsigned char g_static_scratch[BC_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the runtime; the address kernels can use
+// comes from cudaGetSymbolAddress, once per device, with that device current.
+static void *static_scratch_address(int *status)
+{
+    static std::mutex mutex;
+    static void *address[64] = {nullptr};
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        *status = check_launch("bc_boxconv2d_backward_static: cudaGetDevice");
+        if (*status == BC_OK) *status = BC_ERR_UNSUPPORTED;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!address[device]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
+            *status = check_launch("bc_boxconv2d_backward_static: cudaGetSymbolAddress");
+            if (*status == BC_OK) *status = BC_ERR_CUDA;
+            return nullptr;
+        }
+        address[device] = p;
+    }
+    *status = BC_OK;
+    return address[device];
+}
+
+int bc_boxconv2d_backward_static(const float *input, const float *x_min, const float *x_max,
+                                 const float *y_min, const float *y_max, const float *grad_output,
+                                 float reparametrization_h, float reparametrization_w, int N, int C,
+                                 int F, int h, int w, int normalize, int exact, int need_mask,
+                                 float *grad_input, float *grad_params, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    const size_t need = bc_boxconv2d_backward_workspace(N, C, F, h, w, need_mask);
+    if (need > BC_STATIC_SCRATCH_BYTES) {
+        snprintf(g_last_error, sizeof(g_last_error),
+                 "bc_boxconv2d_backward_static: this problem needs %zu bytes of scratch, the built-in array has %u",
+                 need, (unsigned)BC_STATIC_SCRATCH_BYTES);
+        return BC_ERR_WORKSPACE;
+    }
+    int status = BC_OK;
+    void *scratch = static_scratch_address(&status);
+    if (!scratch) return status;
+    return bc_boxconv2d_backward(input, x_min, x_max, y_min, y_max, grad_output, reparametrization_h,
+                                 reparametrization_w, N, C, F, h, w, normalize, exact, need_mask,
+                                 grad_input, grad_params, scratch, BC_STATIC_SCRATCH_BYTES, stream);
+}
+
 uint64_t bc_launch_count(void) { return g_launches.load(); }
 
 int bc_wait_timeouts(int *count)

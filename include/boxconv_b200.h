@@ -120,6 +120,33 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                           float *grad_input, float *grad_params, void *workspace,
                           size_t workspace_bytes, bc_stream_t stream);
 
+/* ---- backward pass without caller-supplied scratch memory --------------------------------
+ * This entry point has no counterpart in the reference (which allocates its temporaries with
+ * at::empty on every call).  It is bc_boxconv2d_backward() for hosts that have no way to hand
+ * over a workspace at the moment the gradient is needed and must not allocate one either: a
+ * plugin invoked inside somebody else's stream capture (cudaMalloc is not allowed while a stream
+ * is capturing), a serving process whose device memory was carved up completely at start-up, or
+ * a callback running where the CUDA allocator may not be re-entered.  The scratch memory is a
+ * fixed array of BC_STATIC_SCRATCH_BYTES that is part of the library image: every GPU that loads
+ * the library holds it until the process exits.
+ *
+ *  - Problems whose scratch need (bc_boxconv2d_backward_workspace()) exceeds the array are
+ *    refused with BC_ERR_WORKSPACE; nothing is launched.  Planes that fit in shared memory need
+ *    20 bytes per (sample, plane, filter), so the array covers N*C*F up to about 200 000; larger
+ *    planes need a full set of integral images and fit only when tiny.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.  No call allocates or frees.
+ *  - All calls on a device share the one array and it keeps what the previous call left.  Nothing
+ *    in it has to start at zero: every word a call reads was written earlier by that same call.
+ *    Two calls that overlap on the GPU (different streams, or graphs replayed concurrently) race
+ *    on it and corrupt each other's parameter gradients: serialise them. */
+#define BC_STATIC_SCRATCH_BYTES (4u << 20)
+int bc_boxconv2d_backward_static(const float *input, const float *x_min, const float *x_max,
+                                 const float *y_min, const float *y_max, const float *grad_output,
+                                 float reparametrization_h, float reparametrization_w, int N, int C,
+                                 int F, int h, int w, int normalize, int exact, int need_mask,
+                                 float *grad_input, float *grad_params, bc_stream_t stream);
+
 /* ---- measurement aids (no counterpart in the reference) ---------------------------------
  * bc_launch_count(): kernels launched by this library since it was loaded.
  * bc_profile_*: while enabled, every kernel launch is bracketed by a pair of CUDA events on the
