@@ -37,6 +37,27 @@ import torch  # noqa: E402
 
 from workloads import CONFIGS, make_workload  # noqa: E402
 
+def stage(msg):
+    """Progress line on stderr (rank 0 only) so that a stalled run shows where it stopped."""
+    if os.environ.get("RANK", "0") == "0":
+        print("[bench %.1fs] %s" % (time.perf_counter() - _T0, msg), file=sys.stderr, flush=True)
+
+
+_T0 = time.perf_counter()
+
+
+def arm_watchdog(seconds):
+    """Ends the process from the host side if the run takes longer than `seconds` (a stuck
+    collective or rendezvous must not keep a GPU box busy for its whole time limit)."""
+    def fire():
+        print("[bench] watchdog: no result after %d s, giving up" % seconds, file=sys.stderr, flush=True)
+        os._exit(3)
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
+
+
 METRIC = "BoxConv2d fwd+bwd output Gelem/s"
 UNIT = "Gelem/s"
 BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds the 126 MB L2
@@ -209,6 +230,7 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    stage("process group ready (world %d)" % world)
     sampler = ClockSampler(local_rank)
     sampler.start()
 
@@ -233,16 +255,21 @@ def run_ours(args, rank, world, local_rank):
             xs.append(torch.randn((N, C, h, w), device=dev, generator=gen).requires_grad_())
             gos.append(torch.randn((N, C * F, h, w), device=dev, generator=gen))
 
-    def step(s):
+    def compute(s):
         for p in params:
             p.grad = None
         xs[s].grad = None
         out = module(xs[s])
         out.backward(gos[s])
+        return out
+
+    def step(s):
+        out = compute(s)
         if world > 1:
             bc.allreduce_box_gradients(module)
         return out
 
+    stage("eager warm-up")
     # ---- warm-up (eager), then capture one CUDA graph per buffer set
     for i in range(max(args.warmup, 3)):
         step(i % BUFFER_SETS)
@@ -252,8 +279,11 @@ def run_ours(args, rank, world, local_rank):
     launches_per_step = _cabi.lib.bc_launch_count() - launches_before
     torch.cuda.synchronize()
 
-    graphs = None
+    # The graphs hold the compute of a step (clip, forward, backward); the all-reduce of the packed
+    # parameter gradient is issued after each replay on the same stream, outside the graph.
+    graphs, packed = None, []
     if not args.no_graph:
+        stage("capturing %d CUDA graphs" % BUFFER_SETS)
         graphs, keep = [], []
         pool = None
         for s in range(BUFFER_SETS):
@@ -262,21 +292,43 @@ def run_ours(args, rank, world, local_rank):
                 p.grad = None
             xs[s].grad = None
             with torch.cuda.graph(g, pool=pool):
-                keep.append(step(s))
+                keep.append(compute(s))
+                packed.append(bc.packed_box_gradient(module)[0])
             pool = g.pool()
             graphs.append(g)
         for s in range(BUFFER_SETS):
             graphs[s].replay()
         torch.cuda.synchronize()
 
+    # With graphs, the all-reduce of step k runs on a side stream while step k+1 computes (the way a
+    # trainer overlaps gradient reduction with the rest of the backward pass); a buffer set is not
+    # reused before its reduction has finished, and the timed region ends only when all are done.
+    comm_stream = torch.cuda.Stream(dev) if world > 1 else None
+    reduced = [None] * BUFFER_SETS
+
     def run_steps(k):
+        main = torch.cuda.current_stream()
         for i in range(k):
+            s = i % BUFFER_SETS
             if graphs is not None:
-                graphs[i % BUFFER_SETS].replay()
+                if reduced[s] is not None:
+                    main.wait_event(reduced[s])
+                graphs[s].replay()
+                if world > 1:
+                    ready = torch.cuda.Event()
+                    ready.record(main)
+                    with torch.cuda.stream(comm_stream):
+                        comm_stream.wait_event(ready)
+                        dist.all_reduce(packed[s])
+                        reduced[s] = torch.cuda.Event()
+                        reduced[s].record(comm_stream)
             else:
-                step(i % BUFFER_SETS)
+                step(s)
+        if comm_stream is not None:
+            main.wait_stream(comm_stream)
 
     # ---- the timed region
+    stage("timed region: %d steps" % args.steps)
     run_steps(max(args.warmup, 3))
     if world > 1:
         dist.barrier()
@@ -298,6 +350,7 @@ def run_ours(args, rank, world, local_rank):
     ms_per_step = ms_total / args.steps
     value = wl.outputs * world / (ms_per_step * 1e-3) / 1e9
 
+    stage("eager repeat with per-kernel events")
     # ---- per-kernel device times: the same steps, eagerly, with the library's event pairs
     roofline = None
     eager_ms = None
@@ -336,6 +389,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end: pinned host buffers in, host results out, through the module
     e2e = None
+    stage("end-to-end leg")
     if not args.skip_e2e:
         hx = torch.from_numpy(wl.x).pin_memory()
         hgo = torch.from_numpy(wl.grad_output).pin_memory()
@@ -374,6 +428,7 @@ def run_ours(args, rank, world, local_rank):
         clocks = wider
 
     cpu_baseline = None
+    stage("cpu baseline")
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         ref = CpuReference()
         n = ref.pick_sample(args.workload, 6, 20.0)
@@ -394,7 +449,7 @@ def run_ours(args, rank, world, local_rank):
             "config": {"workload": describe(args.workload), "global_batch": N * world,
                        "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (
                            BUFFER_SETS, wl.algorithmic_bytes / 1e6),
-                       "launch": "eager" if graphs is None else "cuda graph replay, one graph per buffer set",
+                       "launch": "eager" if graphs is None else "cuda graph replay of clip+forward+backward, one graph per buffer set" + ("; all-reduce of step k on a side stream, overlapping step k+1" if world > 1 else ""),
                        "eager_ms_per_step": eager_ms,
                        "collective": "nccl all_reduce of the packed (4,C,F) parameter gradient" if world > 1 else "none"},
             "hbm_gbs_step": wl.algorithmic_bytes * world / (ms_per_step * 1e-3) / 1e9,
@@ -402,7 +457,9 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    stage("done")
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -417,7 +474,9 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=4)
+    ap.add_argument("--max-seconds", type=int, default=600, help="host-side watchdog for the whole run")
     args = ap.parse_args()
+    arm_watchdog(args.max_seconds)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
