@@ -19,8 +19,7 @@ namespace bc {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kWarps = kThreads / 32;
+constexpr int kMaxThreads = 256;
 
 __device__ __forceinline__ float warp_inclusive_scan(float v, int lane)
 {
@@ -32,8 +31,46 @@ __device__ __forceinline__ float warp_inclusive_scan(float v, int lane)
     return v;
 }
 
-template <bool VEC4>
-__global__ void __launch_bounds__(kThreads)
+constexpr int kBatch = 8;      // 128-bit loads a lane keeps in flight: 8 x 32 lanes x 16 B = one 1024-float row
+
+// Loads kBatch consecutive 128-column segments of a row, starting at segment seg0.
+__device__ __forceinline__ void load_segments(const float4 *row4, int n4, int seg0, int lane, float4 (&buf)[kBatch])
+{
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+        const int j = (seg0 + k) * 32 + lane;
+        buf[k] = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+// Prefix-sums the loaded segments along the row (carry `running` joins segments and batches) and
+// writes them to the tile row at columns c+1.
+__device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n4, int seg0, int lane, int w,
+                                              float *trow, float &running)
+{
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+        if ((seg0 + k) * 32 < n4) {
+            float4 v = buf[k];
+            v.y += v.x; v.z += v.y; v.w += v.z;
+            const float incl = warp_inclusive_scan(v.w, lane);
+            const float add = running + (incl - v.w);
+            running += __shfl_sync(0xffffffffu, incl, 31);
+            const int c = ((seg0 + k) * 32 + lane) << 2;
+            if (c < w) {
+                trow[c + 1] = v.x + add; trow[c + 2] = v.y + add;
+                trow[c + 3] = v.z + add; trow[c + 4] = v.w + add;
+            }
+        }
+    }
+}
+
+// PIPELINED (rows of 512..1024 floats, one row per warp): a lane keeps a whole row of 128-bit loads
+// in flight and the next tile's row is fetched while the current tile is scanned down its columns
+// and stored, so a CTA always has a full tile of loads outstanding.  Otherwise (short rows, many
+// planes) the kernel stays small in registers and relies on many resident CTAs.
+template <bool VEC4, bool PIPELINED>
+__global__ void __launch_bounds__(kMaxThreads)
 integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int h, int w, int tile_rows)
 {
     extern __shared__ float4 smem4[];
@@ -42,9 +79,14 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     float *carry = tile + ((tile_rows * pw + 4 + 3) & ~3);    // w floats
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kThreads = blockDim.x, kWarps = blockDim.x >> 5;
     const int64_t plane = blockIdx.x;
     const float *src = in + plane * (int64_t)h * w;
     float *dst = out + plane * (int64_t)(h + 1) * pw;
+    const int n4 = w >> 2;
+    float4 pre[kBatch];      // dead in the instantiations that are not PIPELINED
+    if (PIPELINED && warp < tile_rows && warp < h)
+        load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre);
 
     for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
     for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
@@ -56,46 +98,68 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
         float *t = tile + mis;
 
         // ---- 1. row pass
-        for (int i = warp; i < rows; i += kWarps) {
-            const float *row = src + (int64_t)(r0 + i) * w;
-            float *trow = t + i * pw;
-            if (lane == 0) trow[0] = 0.0f;
-            float running = 0.0f;
-            if (VEC4) {
-                const float4 *row4 = reinterpret_cast<const float4 *>(row);
-                const int n4 = w >> 2;
-                float4 nxt = lane < n4 ? __ldg(row4 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int c4 = 0; c4 < n4; c4 += 32) {
-                    float4 v = nxt;
-                    const int j = c4 + 32 + lane;
-                    if (c4 + 32 < n4) nxt = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    v.y += v.x; v.z += v.y; v.w += v.z;
-                    const float incl = warp_inclusive_scan(v.w, lane);
-                    const float add = running + (incl - v.w);
-                    running += __shfl_sync(0xffffffffu, incl, 31);
-                    const int c = (c4 + lane) << 2;
-                    if (c < w) {
-                        trow[c + 1] = v.x + add; trow[c + 2] = v.y + add;
-                        trow[c + 3] = v.z + add; trow[c + 4] = v.w + add;
+        if (PIPELINED) {
+            if (warp < rows) {
+                float *trow = t + warp * pw;
+                if (lane == 0) trow[0] = 0.0f;
+                float running = 0.0f;
+                scan_segments(pre, n4, 0, lane, w, trow, running);
+            }
+            const int rn = r0 + tile_rows + warp;
+            if (warp < tile_rows && rn < h)
+                load_segments(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, 0, lane, pre);
+        } else {
+            for (int i = warp; i < rows; i += kWarps) {
+                const float *row = src + (int64_t)(r0 + i) * w;
+                float *trow = t + i * pw;
+                if (lane == 0) trow[0] = 0.0f;
+                float running = 0.0f;
+                if (VEC4) {
+                    const float4 *row4 = reinterpret_cast<const float4 *>(row);
+                    float4 nxt = lane < n4 ? __ldg(row4 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int c4 = 0; c4 < n4; c4 += 32) {
+                        float4 v = nxt;
+                        const int j = c4 + 32 + lane;
+                        if (c4 + 32 < n4) nxt = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v.y += v.x; v.z += v.y; v.w += v.z;
+                        const float incl = warp_inclusive_scan(v.w, lane);
+                        const float add = running + (incl - v.w);
+                        running += __shfl_sync(0xffffffffu, incl, 31);
+                        const int c = (c4 + lane) << 2;
+                        if (c < w) {
+                            trow[c + 1] = v.x + add; trow[c + 2] = v.y + add;
+                            trow[c + 3] = v.z + add; trow[c + 4] = v.w + add;
+                        }
                     }
-                }
-            } else {
-                for (int c0 = 0; c0 < w; c0 += 32) {
-                    const int c = c0 + lane;
-                    const float v = c < w ? __ldg(row + c) : 0.0f;
-                    const float incl = warp_inclusive_scan(v, lane);
-                    if (c < w) trow[c + 1] = incl + running;
-                    running += __shfl_sync(0xffffffffu, incl, 31);
+                } else {
+                    for (int c0 = 0; c0 < w; c0 += 32) {
+                        const int c = c0 + lane;
+                        const float v = c < w ? __ldg(row + c) : 0.0f;
+                        const float incl = warp_inclusive_scan(v, lane);
+                        if (c < w) trow[c + 1] = incl + running;
+                        running += __shfl_sync(0xffffffffu, incl, 31);
+                    }
                 }
             }
         }
         __syncthreads();
 
-        // ---- 2. column pass
+        // ---- 2. column pass (8 rows at a time in registers so that the loads overlap)
         for (int c = tid; c < w; c += kThreads) {
             float run = carry[c];
             float *col = t + c + 1;
-            for (int i = 0; i < rows; ++i) {
+            int i = 0;
+            for (; i + 8 <= rows; i += 8) {
+                float v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = col[(i + k) * pw];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    run += v[k];
+                    col[(i + k) * pw] = run;
+                }
+            }
+            for (; i < rows; ++i) {
                 run += col[i * pw];
                 col[i * pw] = run;
             }
@@ -122,26 +186,36 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
 
 }  // namespace
 
+// Shared memory a CTA needs for tiles of `tile_rows` rows.
+static size_t tile_smem_bytes(int tile_rows, int w)
+{
+    return ((size_t)((tile_rows * (w + 1) + 4 + 3) & ~3) + (size_t)w) * sizeof(float);
+}
+
 int launch_integral_image(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
 {
     if (planes == 0) return BC_OK;
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const int pw = w + 1;
+    const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
     // rows per tile: about 36 KB of shared memory, never more than the plane has
     int tile_rows = 9000 / pw;
+    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && h >= 2 * (kMaxThreads / 32);
+    if (pipelined) tile_rows = kMaxThreads / 32;
     if (tile_rows < 1) tile_rows = 1;
-    if (tile_rows > h) tile_rows = h;
-    const size_t smem = ((size_t)((tile_rows * pw + 4 + 3) & ~3) + (size_t)w) * sizeof(float);
+    if (tile_rows > h) tile_rows = h > 0 ? h : 1;
+    const size_t smem = tile_smem_bytes(tile_rows, w);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
-    const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
-    auto kern = vec4 ? integral_image_kernel<true> : integral_image_kernel<false>;
+    void (*kern)(const float *, float *, int, int, int) =
+        pipelined ? integral_image_kernel<true, true>
+                  : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("integral_image: shared memory opt-in");
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
-        kern<<<(unsigned)planes, kThreads, smem, s>>>(in, out, h, w, tile_rows);
+        kern<<<(unsigned)planes, kMaxThreads, smem, s>>>(in, out, h, w, tile_rows);
     }
     return check_launch("integral_image");
 }
