@@ -220,6 +220,63 @@ def kernel_algorithmic_bytes(kernel, N, C, F, h, w):
     }.get(kernel)
 
 
+def run_integral(args, rank, world, local_rank):
+    """cfg4: the integral image alone, 1024 planes of 512 x 1024 U[0,1) per GPU."""
+    import box_convolution as bc
+    from box_convolution import _cabi
+    from workloads import make_integral_workload
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    planes, h, w = 1024, 512, 1024
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1004 + rank)
+    x = torch.rand((planes, h, w), device=dev, generator=gen)
+    out = torch.empty((planes, h + 1, w + 1), device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        _cabi.check(_cabi.lib.bc_integral_image(x.data_ptr(), out.data_ptr(), planes, h, w, stream), "integral_image")
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    alg = 4 * planes * (h * w + (h + 1) * (w + 1))
+    peak, peak_src = measured_peak()
+    achieved = alg / (ms * 1e-3) / 1e9
+    cpu_baseline = None
+    if rank == 0 and not args.skip_cpu_baseline:
+        ref = CpuReference()
+        sample = make_integral_workload(planes=64, h=h, w=w)
+        t = torch.from_numpy(sample)
+        fn = (lambda: ref.ext.integral_image(t)) if ref.ext is not None else (lambda: ref.oracle.integral_image(sample))
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            fn()
+        sec = (time.perf_counter() - t0) / 5
+        cpu_baseline = {"value": 4 * 64 * (h * w + (h + 1) * (w + 1)) / sec / 1e9, "unit": "GB/s", "cores": ref.cores,
+                        "kind": ref.kind, "sample": "64 of 1024 planes, 1 warm-up + 5 runs, mean %.3f s" % sec}
+    if rank == 0:
+        print(json.dumps({
+            "metric": "integral_image algorithmic HBM GB/s", "value": achieved * world, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg4: integral image of 1024 planes of 512x1024 per GPU, U[0,1)",
+                       "l2": "4.3 GB touched per launch"},
+            "roofline": {"bound": "hbm", "kernel": "integral_image_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "algorithmic_bytes": alg,
+                         "mean_us": ms * 1e3, "peak_source": peak_src},
+            "cpu_baseline": cpu_baseline, "gpu_launches": args.steps}), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     import box_convolution as bc
@@ -469,7 +526,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS) + ["cfg4"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
@@ -485,11 +542,16 @@ def main():
         raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node %d bench.py --gpus %d ..."
                          % (args.gpus, args.gpus))
     if args.impl == "reference":
+        if args.workload == "cfg4":
+            raise SystemExit("--impl reference supports the BoxConv2d workloads; cfg4 prints its CPU baseline in the main line")
         run_reference(args, rank, world)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py --impl ours needs a GPU: the CUDA library has no CPU fallback")
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "cfg4":
+            run_integral(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":
