@@ -473,7 +473,7 @@ def run_ours(args, rank, world, local_rank):
                "h2d_bytes_per_step": hx.numel() * 4 + hgo.numel() * 4,
                "d2h_bytes_per_step": (hout.numel() + hgin.numel() + hgp.numel()) * 4,
                "ms_per_step": sec * 1e3, "steps": k_e2e, "chunks": args.e2e_chunks,
-               "api": "box_convolution.HostPipeline.step (BoxConv2d forward/backward per batch chunk, copies on side streams)"}
+               "api": "box_convolution.HostPipeline.step -> bc_boxconv2d_host_step (C ABI, pinned host buffers in and out, chunked copy/compute overlap on 3 streams)"}
         t_busy_end = time.perf_counter()
 
     sampler.stop_flag = True
@@ -530,7 +530,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=4)
+    ap.add_argument("--e2e-chunks", type=int, default=8)
     ap.add_argument("--max-seconds", type=int, default=600, help="host-side watchdog for the whole run")
     args = ap.parse_args()
     arm_watchdog(args.max_seconds)

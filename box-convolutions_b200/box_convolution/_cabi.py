@@ -33,6 +33,8 @@ SIGNATURES = {
     "bc_boxconv2d_backward_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_backward": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_boxconv2d_backward_static": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp]),
+    "bc_boxconv2d_host_step_workspace": (_sz, [_i] * 6),
+    "bc_boxconv2d_host_step": (_i, [_vp] * 9 + [_f, _f, _d, _d] + [_i] * 9 + [_vp, _sz, _vp, _vp, _vp]),
     "bc_launch_count": (ctypes.c_uint64, []),
     "bc_wait_timeouts": (_i, [ctypes.POINTER(_i)]),
     "bc_profile_start": (_i, [_i]),

@@ -349,6 +349,7 @@ const char *bc_kernel_name(int kernel_id)
         case KID_CLIP: return "clip_kernel";
         case KID_FORWARD_PLANE: return "forward_plane_kernel";
         case KID_BACKWARD_PLANE: return "backward_plane_kernel";
+        case KID_SUM_CHUNKS: return "sum_chunk_grads_kernel";
         default: return "unknown";
     }
 }

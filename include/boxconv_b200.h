@@ -120,6 +120,26 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                           float *grad_input, float *grad_params, void *workspace,
                           size_t workspace_bytes, bc_stream_t stream);
 
+/* ---- a whole training step on a batch in host memory -------------------------------------
+ * What a caller of the reference does around the module when its data sit in host memory
+ * (copy in, BoxConv2d.forward with its parameter clip, backward, copy out:
+ * box_convolution/box_convolution_module.py:216-222, box_convolution_function.py:32-65), as one
+ * call on HOST buffers: x (N,C,h,w) and grad_output (N,C*F,h,w) in, output, grad_input and the
+ * packed (4,C,F) parameter gradient out.  The batch is processed in `chunks` pieces whose copies
+ * and kernels overlap on the three streams given; host buffers should be pinned.  The four
+ * parameter arrays are device memory in stored units and are clipped in place when clip != 0.
+ * The call only enqueues work: results are complete once `copy_out` has been synchronised, and
+ * that must happen before the next call that uses the same workspace.  The workspace (device
+ * memory, 256-byte aligned, size from the query) holds the device copies of all tensors. */
+size_t bc_boxconv2d_host_step_workspace(int N, int C, int F, int h, int w, int chunks);
+int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, float *out_host,
+                           float *grad_input_host, float *grad_params_host, float *x_min, float *x_max,
+                           float *y_min, float *y_max, float reparametrization_h,
+                           float reparametrization_w, double max_input_h, double max_input_w, int N,
+                           int C, int F, int h, int w, int normalize, int exact, int clip, int chunks,
+                           void *workspace, size_t workspace_bytes, bc_stream_t copy_in,
+                           bc_stream_t compute, bc_stream_t copy_out);
+
 /* ---- backward pass without caller-supplied scratch memory --------------------------------
  * This entry point has no counterpart in the reference (which allocates its temporaries with
  * at::empty on every call).  It is bc_boxconv2d_backward() for hosts that have no way to hand
