@@ -63,7 +63,13 @@ UNIT = "Gelem/s"
 BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds the 126 MB L2
 # DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
 # profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    # profiles/plane_kernels_cfg2_ncu_full.md: 83.93 MB read + 3.82 MB written on cfg2 (4 194 304 input
+    # elements); below the 100.7 MB algorithmic figure because the 126 MB L2 still holds part of the
+    # 16.8 MB grad_input when the kernel ends
+    "backward_plane_kernel": (87.76e6, 4194304),
+    "forward_plane_kernel": (25.99e6, 4194304),
+}
 
 
 def describe(name):
@@ -272,7 +278,9 @@ def run_integral(args, rank, world, local_rank):
             "config": {"workload": "cfg4: integral image of 1024 planes of 512x1024 per GPU, U[0,1)",
                        "l2": "4.3 GB touched per launch"},
             "roofline": {"bound": "hbm", "kernel": "integral_image_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "algorithmic_bytes": alg,
+                         "unit": "GB/s", "frac": achieved / peak,
+                         # profiles/integral_image_kernel_cfg4_ncu.md: 2.148 GB read + 2.108 GB written
+                         "traffic": 4.2556e9, "algorithmic_bytes": alg,
                          "mean_us": ms * 1e3, "peak_source": peak_src},
             "cpu_baseline": cpu_baseline, "gpu_launches": args.steps}), flush=True)
 
