@@ -206,6 +206,29 @@ def test_module_random_shapes_vs_oracle(bc, shape, normalize, exact):
         assert (out.detach().view(N, C, F, h, w)[:, 0, 0] == 0).all()
 
 
+def test_many_filters_take_the_general_path(bc):
+    """More filters than the per-CTA tap table holds: the module falls back to the kernels that
+    read integral images from global memory; results must not change."""
+    rng = np.random.default_rng(4)
+    N, C, F, h, w = 1, 2, 33, 16, 20
+    x = rng.standard_normal((N, C, h, w)).astype(np.float32)
+    go = rng.standard_normal((N, C * F, h, w)).astype(np.float32)
+    cx = rng.uniform(-h / 2, h / 2, (C, F)); ex = rng.uniform(0.6, h / 3, (C, F))
+    cy = rng.uniform(-w / 2, w / 2, (C, F)); ey = rng.uniform(0.6, w / 3, (C, F))
+    pix = [a.astype(np.float32) for a in (cx - ex, cx + ex, cy - ey, cy + ey)]
+    params = [cuda(p).requires_grad_() for p in pix]
+    xt = cuda(x).requires_grad_()
+    out = bc.BoxConvolutionFunction.apply(xt, *params, 1.0, 1.0, True, True)
+    out.backward(cuda(go))
+    integ = oracle.integral_image(x)
+    ref_out = oracle.box_convolution_forward(integ, *pix, True, True)
+    ref = oracle.box_convolution_backward(integ, *pix, go, ref_out, 1.0, 1.0, True, True)
+    assert max_rel(out.detach().cpu().numpy(), ref_out) < TOL_OUT
+    assert max_rel(xt.grad.cpu().numpy(), ref[0]) < TOL_GIN
+    for k in range(4):
+        assert max_rel(params[k].grad.cpu().numpy(), ref[1 + k]) < TOL_PARAM, k
+
+
 def test_eval_mode_clips_once_and_matches(bc):
     wl = make_workload("cfg1", batch=2)
     m = bc.BoxConv2d(16, 4, 64, 64).cuda()
