@@ -772,6 +772,7 @@ int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N,
     // (each part rebuilds the integral image; the second read of the plane comes from L2).
     int fsplit = 1;
     if (F % 2 == 0 && planes < 148 * 6) fsplit = 2;
+    while (fsplit < F && F % (fsplit * 2) == 0 && planes * fsplit * 2 <= 148 * 2) fsplit *= 2;   // tiny batches: fill the SMs
     if (planes * fsplit > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const size_t smem = forward_smem_bytes(h, w);
     const int tiles = warp_tiles(h, w);
