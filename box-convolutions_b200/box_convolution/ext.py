@@ -1,7 +1,8 @@
 """The four functions of the reference's compiled module ``box_convolution_cpp_cuda``
 (``src/bind.cpp:29-34``), with the same names, argument order and return values, served by the
 sm_100a library.  Code written against ``box_convolution_cpp_cuda`` can import this module in
-its place.  Tensors must be CUDA float32; there is no CPU implementation.
+its place.  Tensors must be CUDA float32 or float64 (all arguments of one call in the same type);
+there is no CPU implementation.
 """
 import torch
 
@@ -13,20 +14,28 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _require_cuda_f32(t, name):
+def _require_cuda_float(t, name, dtype=None):
+    """CUDA tensor of float32 or float64 (of `dtype` when given)."""
     if not isinstance(t, torch.Tensor):
         raise TypeError("%s must be a tensor" % name)
     if not t.is_cuda:
         raise RuntimeError("box_convolution: %s is not a CUDA tensor; this build has no CPU implementation" % name)
-    if t.dtype != torch.float32:
-        raise RuntimeError("box_convolution: %s must be float32, got %s" % (name, t.dtype))
+    if t.dtype not in (torch.float32, torch.float64):
+        raise RuntimeError("box_convolution: %s must be float32 or float64, got %s" % (name, t.dtype))
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("box_convolution: %s is %s but the call's other tensors are %s" % (name, t.dtype, dtype))
 
 
-def _check_params(x_min, x_max, y_min, y_max, in_planes, prefix):
+def _entry(name, dtype):
+    """The library function `name` for `dtype`."""
+    return getattr(lib, name + ("_f64" if dtype == torch.float64 else ""))
+
+
+def _check_params(x_min, x_max, y_min, y_max, in_planes, prefix, dtype):
     # same conditions and wording as src/box_convolution_interface.cpp:24-34,159-170
     ps = (x_min, x_max, y_min, y_max)
     for p, n in zip(ps, ("x_min", "x_max", "y_min", "y_max")):
-        _require_cuda_f32(p, n)
+        _require_cuda_float(p, n, dtype)
     if not all(p.dim() == 2 for p in ps):
         raise RuntimeError(prefix + "all parameters must have 2 dimensions")
     if not all(p.size(0) == in_planes for p in ps):
@@ -44,7 +53,7 @@ def _workspace(nbytes, device):
 def integral_image(input):
     """(..., h, w) -> (..., h+1, w+1) zero-padded 2-D prefix sum.
     Mirrors src/integral_image_interface.cpp:8-27."""
-    _require_cuda_f32(input, "input")
+    _require_cuda_float(input, "input")
     if input.dim() < 2:
         raise RuntimeError("integral image input must have >=2 dimensions")
     input = input.contiguous()
@@ -52,25 +61,26 @@ def integral_image(input):
     out = torch.empty(input.shape[:-2] + (h + 1, w + 1), dtype=input.dtype, device=input.device)
     planes = input.numel() // (h * w) if h * w else (out.numel() // ((h + 1) * (w + 1)))
     with torch.cuda.device(input.device):
-        check(lib.bc_integral_image(input.data_ptr(), out.data_ptr(), planes, h, w, _stream()), "integral_image")
+        check(_entry("bc_integral_image", input.dtype)(input.data_ptr(), out.data_ptr(), planes, h, w, _stream()), "integral_image")
     return out
 
 
 def box_convolution_forward(input_integrated, x_min, x_max, y_min, y_max, normalize, exact):
     """Mirrors src/box_convolution_interface.cpp:13-139.  Parameters are in actual pixels."""
-    _require_cuda_f32(input_integrated, "input_integrated")
+    _require_cuda_float(input_integrated, "input_integrated")
+    dtype = input_integrated.dtype
     if input_integrated.device != x_min.device:
         raise RuntimeError("BoxConv2d: input and parameters are on different devices")
     input_integrated = input_integrated.contiguous()
     if input_integrated.dim() != 4:
         raise RuntimeError("BoxConv2d: input must have 4 dimensions")
-    ps = _check_params(x_min, x_max, y_min, y_max, input_integrated.size(1), "BoxConv2d: ")
+    ps = _check_params(x_min, x_max, y_min, y_max, input_integrated.size(1), "BoxConv2d: ", dtype)
     N, C, hp, wp = input_integrated.shape
     F = ps[0].size(1)
     h, w = hp - 1, wp - 1
-    out = torch.empty((N, C, F, h, w), dtype=torch.float32, device=input_integrated.device)
+    out = torch.empty((N, C, F, h, w), dtype=dtype, device=input_integrated.device)
     with torch.cuda.device(out.device):
-        check(lib.bc_box_convolution_forward(
+        check(_entry("bc_box_convolution_forward", dtype)(
             input_integrated.data_ptr(), *[p.data_ptr() for p in ps], out.data_ptr(),
             N, C, F, h, w, int(bool(normalize)), int(bool(exact)), _stream()), "box_convolution_forward")
     return out.reshape(N, C * F, h, w)
@@ -83,8 +93,9 @@ def box_convolution_backward(
     """Mirrors src/box_convolution_interface.cpp:141-395: returns
     [grad_input, grad_x_min, grad_x_max, grad_y_min, grad_y_max]; entries not asked for are
     0-element tensors (interface.cpp:182,394).  `output` is accepted and ignored."""
-    _require_cuda_f32(input_integrated, "input_integrated")
-    _require_cuda_f32(grad_output, "grad_output")
+    _require_cuda_float(input_integrated, "input_integrated")
+    dtype = input_integrated.dtype
+    _require_cuda_float(grad_output, "grad_output", dtype)
     grad_output = grad_output.contiguous()
     input_integrated = input_integrated.contiguous()
     if grad_output.dim() != 4:
@@ -93,7 +104,7 @@ def box_convolution_backward(
         raise RuntimeError("BoxConv2d: input must have 4 dimensions")
     N, C, hp, wp = input_integrated.shape
     h, w = hp - 1, wp - 1
-    ps = _check_params(x_min, x_max, y_min, y_max, C, "")
+    ps = _check_params(x_min, x_max, y_min, y_max, C, "", dtype)
     F = ps[0].size(1)
     # the reference checks the height twice and never the width (interface.cpp:157-158); both here
     if tuple(grad_output.shape) != (N, C * F, h, w):
@@ -102,12 +113,12 @@ def box_convolution_backward(
     mask = sum(1 << i for i, b in enumerate(needs) if b)
     dev = input_integrated.device
     null = torch.empty(0)
-    grad_input = torch.empty((N, C, h, w), dtype=torch.float32, device=dev) if needs[0] else None
-    grad_params = torch.empty((4, C, F), dtype=torch.float32, device=dev) if any(needs[1:]) else None
+    grad_input = torch.empty((N, C, h, w), dtype=dtype, device=dev) if needs[0] else None
+    grad_params = torch.empty((4, C, F), dtype=dtype, device=dev) if any(needs[1:]) else None
     if mask:
         with torch.cuda.device(dev):
-            ws = _workspace(lib.bc_box_convolution_backward_workspace(N, C, F, h, w, mask), dev)
-            check(lib.bc_box_convolution_backward(
+            ws = _workspace(_entry("bc_box_convolution_backward_workspace", dtype)(N, C, F, h, w, mask), dev)
+            check(_entry("bc_box_convolution_backward", dtype)(
                 input_integrated.data_ptr(), *[p.data_ptr() for p in ps], grad_output.data_ptr(), None,
                 float(reparametrization_h), float(reparametrization_w), N, C, F, h, w,
                 int(bool(normalize)), int(bool(exact)), mask,
@@ -122,13 +133,13 @@ def clip_parameters(x_min, x_max, y_min, y_max, reparametrization_h, reparametri
     """In place.  Mirrors src/box_convolution_interface.cpp:397-415."""
     ps = (x_min, x_max, y_min, y_max)
     for p, n in zip(ps, ("x_min", "x_max", "y_min", "y_max")):
-        _require_cuda_f32(p, n)
+        _require_cuda_float(p, n, x_min.dtype if isinstance(x_min, torch.Tensor) else None)
         if not p.is_contiguous():
             raise RuntimeError("%s must be contiguous" % n)
     if not all(p.numel() == x_min.numel() for p in ps):
         raise RuntimeError("box_convolution: parameter tensors differ in size")
     with torch.cuda.device(x_min.device):
-        check(lib.bc_clip_parameters(
+        check(_entry("bc_clip_parameters", x_min.dtype)(
             *[p.data_ptr() for p in ps], x_min.numel(), float(reparametrization_h),
             float(reparametrization_w), float(max_input_h), float(max_input_w),
             int(bool(exact)), _stream()), "clip_parameters")

@@ -6,12 +6,16 @@ integral image or the output for the backward pass: the fused entry points work 
 itself (integral images live on chip for planes that fit there) and the term the reference
 takes from the saved output is recomputed, so only the input and the four parameter tensors are
 kept alive between forward and backward.
+
+float64 tensors (gradient checks) take the general kernels through the four extension functions,
+chained as the reference chains them.
 """
 import torch
 
 from . import _cabi
 from ._cabi import check, lib
-from .ext import _require_cuda_f32, _stream, _workspace
+from . import ext
+from .ext import _require_cuda_float, _stream, _workspace
 
 
 def reparametrize(x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
@@ -37,12 +41,12 @@ class BoxConvolutionFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, x_min, x_max, y_min, y_max,
                 reparametrization_h, reparametrization_w, normalize, exact):
-        _require_cuda_f32(input, "input")
+        _require_cuda_float(input, "input")
         if input.dim() != 4:
             raise RuntimeError("BoxConv2d: input must have 4 dimensions")
         params = (x_min, x_max, y_min, y_max)
         for p, n in zip(params, ("x_min", "x_max", "y_min", "y_max")):
-            _require_cuda_f32(p, n)
+            _require_cuda_float(p, n, input.dtype)
             if p.device != input.device:
                 raise RuntimeError("BoxConv2d: input and parameters are on different devices")
         if not all(p.dim() == 2 for p in params):
@@ -56,6 +60,16 @@ class BoxConvolutionFunction(torch.autograd.Function):
 
         input = input.contiguous()
         params = [p.detach().contiguous() for p in params]
+        ctx.normalize, ctx.exact = bool(normalize), bool(exact)
+        ctx.reparametrization_h, ctx.reparametrization_w = reparametrization_h, reparametrization_w
+        ctx.chained = input.dtype == torch.float64
+        if ctx.chained:
+            # box_convolution_function.py:36-49 of the reference: pixels, integral image, gather
+            pixels = reparametrize(*params, reparametrization_h, reparametrization_w, inverse=True)
+            input_integrated = ext.integral_image(input)
+            out = ext.box_convolution_forward(input_integrated, *pixels, normalize, exact)
+            ctx.save_for_backward(input_integrated, *pixels)
+            return out
         out = torch.empty((N, C * F, h, w), dtype=torch.float32, device=input.device)
         with torch.cuda.device(input.device):
             ws = _workspace(lib.bc_boxconv2d_forward_workspace(N, C, F, h, w), input.device)
@@ -64,14 +78,18 @@ class BoxConvolutionFunction(torch.autograd.Function):
                 float(reparametrization_h), float(reparametrization_w), out.data_ptr(),
                 N, C, F, h, w, int(bool(normalize)), int(bool(exact)),
                 ws.data_ptr(), ws.numel(), _stream()), "BoxConv2d forward")
-
-        ctx.normalize, ctx.exact = bool(normalize), bool(exact)
-        ctx.reparametrization_h, ctx.reparametrization_w = reparametrization_h, reparametrization_w
         ctx.save_for_backward(input, *params)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
+        if ctx.chained:
+            input_integrated, x_min, x_max, y_min, y_max = ctx.saved_tensors
+            needs = ctx.needs_input_grad[:5]
+            grads = ext.box_convolution_backward(
+                input_integrated, x_min, x_max, y_min, y_max, grad_output, None,
+                ctx.reparametrization_h, ctx.reparametrization_w, ctx.normalize, ctx.exact, *needs)
+            return tuple(g if n else None for g, n in zip(grads, needs)) + (None,) * 4
         input, x_min, x_max, y_min, y_max = ctx.saved_tensors
         N, C, h, w = input.shape
         F = x_min.size(1)
@@ -79,7 +97,7 @@ class BoxConvolutionFunction(torch.autograd.Function):
         mask = sum(1 << i for i, b in enumerate(needs) if b)
         grad_input = grad_params = None
         if mask:
-            _require_cuda_f32(grad_output, "grad_output")
+            _require_cuda_float(grad_output, "grad_output", torch.float32)
             grad_output = grad_output.contiguous()
             dev = input.device
             if needs[0]:

@@ -11,18 +11,23 @@ namespace bc {
 
 // The four parameter arrays plus the fp32 factors that turn stored values into pixels
 // (1 for the entry points that already receive pixels).
-struct BoxParams {
-    const float *x_min, *x_max, *y_min, *y_max;
-    float mul_h, mul_w;
+template <typename T>
+struct BoxParamsT {
+    const T *x_min, *x_max, *y_min, *y_max;
+    T mul_h, mul_w;
 };
+using BoxParams = BoxParamsT<float>;
 
-struct Box {
-    float xmin, xmax, ymin, ymax;
+template <typename T>
+struct BoxT {
+    T xmin, xmax, ymin, ymax;
 };
+using Box = BoxT<float>;
 
-__device__ __forceinline__ Box load_box(const BoxParams &p, int k)
+template <typename T>
+__device__ __forceinline__ BoxT<T> load_box(const BoxParamsT<T> &p, int k)
 {
-    Box b;
+    BoxT<T> b;
     b.xmin = __ldg(p.x_min + k) * p.mul_h;
     b.xmax = __ldg(p.x_max + k) * p.mul_h;
     b.ymin = __ldg(p.y_min + k) * p.mul_w;
@@ -49,22 +54,33 @@ struct LaunchScope {
 };
 
 // ---- launchers (one per translation unit) --------------------------------------------------
-int launch_integral_image(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s);
+// (the general kernels exist for float and double; everything else is float only)
+template <typename T>
+int launch_integral_image(const T *in, T *out, int64_t planes, int h, int w, cudaStream_t s);
+template <> int launch_integral_image<float>(const float *, float *, int64_t, int, int, cudaStream_t);
+template <> int launch_integral_image<double>(const double *, double *, int64_t, int, int, cudaStream_t);
 
-int launch_forward_global(const float *integ, const BoxParams &bp, float *out, int N, int C, int F,
+template <typename T>
+int launch_forward_global(const T *integ, const BoxParamsT<T> &bp, T *out, int N, int C, int F,
                           int h, int w, bool normalize, bool exact, cudaStream_t s);
 
 // Backward from integral(grad_output) held in global memory.  Exactly one of x / x_integ is
 // non-null: the input plane values are read from x, or rebuilt from the input's integral image.
-size_t backward_partials_bytes(int N, int C, int F, int h, int w);
-int launch_backward_global(const float *x, const float *x_integ, const float *go_integ,
-                           const BoxParams &bp, float rep_h, float rep_w, int N, int C, int F,
-                           int h, int w, bool normalize, bool exact, int need_mask,
-                           float *grad_input, float *grad_params, float *partials, cudaStream_t s);
+size_t backward_partials_bytes(int N, int C, int F, int h, int w, size_t elem_size = sizeof(float));
+template <typename T>
+int launch_backward_global(const T *x, const T *x_integ, const T *go_integ, const BoxParamsT<T> &bp,
+                           T rep_h, T rep_w, int N, int C, int F, int h, int w, bool normalize,
+                           bool exact, int need_mask, T *grad_input, T *grad_params, T *partials,
+                           cudaStream_t s);
 
-int launch_finish_param_grads(const float *partials, const BoxParams &bp, int count, int per_box,
-                              bool normalize, bool exact, float rep_h, float rep_w, int need_mask,
-                              float *grad_params, cudaStream_t s);
+template <typename T>
+int launch_clip(T *x_min, T *x_max, T *y_min, T *y_max, int count, double rep_h, double rep_w,
+                double max_h, double max_w, bool exact, cudaStream_t s);
+
+template <typename T>
+int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int count, int per_box,
+                              bool normalize, bool exact, T rep_h, T rep_w, int need_mask,
+                              T *grad_params, cudaStream_t s);
 
 // Shared-memory-resident path for small planes (box_plane_smem.cu).
 bool plane_path_fits_forward(int F, int h, int w);
@@ -79,7 +95,5 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
 
 int read_wait_timeouts(int *count);
 
-int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int count, double rep_h,
-                double rep_w, double max_h, double max_w, bool exact, cudaStream_t s);
 
 }  // namespace bc

@@ -27,54 +27,66 @@ namespace bc {
 
 constexpr int kStrip = 4;  // columns per thread
 
+// Scalar type: float on the benchmarked path; double instantiates the general (global-memory)
+// kernels for the reference's float64 use (gradient checks).
+BC_HD float bc_ceil(float v) { return ceilf(v); }
+BC_HD double bc_ceil(double v) { return ceil(v); }
+BC_HD float bc_floor(float v) { return floorf(v); }
+BC_HD double bc_floor(double v) { return floor(v); }
+
 // Integer tap offsets (relative to the pixel) and fractional weights of one box, plus the
 // normalisation factor applied to the gathered value.
-struct BoxTaps {
+template <typename T>
+struct BoxTapsT {
     int lo_r, hi_r, lo_c, hi_c;     // rows: taps lo_r-1, lo_r, hi_r, hi_r+1; columns likewise
-    float f_lo_r, f_hi_r, f_lo_c, f_hi_c;
-    float scale;                    // 1/area when normalising, else 1
+    T f_lo_r, f_hi_r, f_lo_c, f_hi_c;
+    T scale;                        // 1/area when normalising, else 1
 };
+using BoxTaps = BoxTapsT<float>;
 
 BC_HD int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
 // Reciprocal of the box area (or of one side), src/box_convolution.cpp:765-793.  In rounded
 // mode the box is first shrunk to whole pixels.
-BC_HD float inv_area(float xmin, float xmax, float ymin, float ymax, bool exact, bool use_x, bool use_y)
+template <typename T>
+BC_HD T inv_area(T xmin, T xmax, T ymin, T ymax, bool exact, bool use_x, bool use_y)
 {
-    if (!exact) { xmin = ceilf(xmin); ymin = ceilf(ymin); xmax = floorf(xmax); ymax = floorf(ymax); }
-    float a = 1.0f;
-    if (use_x) { float len = xmax - xmin; len += 1.0f; a *= len; }
-    if (use_y) { float len = ymax - ymin; len += 1.0f; a *= len; }
-    return 1.0f / a;
+    if (!exact) { xmin = bc_ceil(xmin); ymin = bc_ceil(ymin); xmax = bc_floor(xmax); ymax = bc_floor(ymax); }
+    T a = T(1);
+    if (use_x) { T len = xmax - xmin; len += T(1); a *= len; }
+    if (use_y) { T len = ymax - ymin; len += T(1); a *= len; }
+    return T(1) / a;
 }
 
 // Forward split, src/box_convolution.cpp:14-40.  Rounded mode keeps the integer taps and drops
 // the fractions (src/box_convolution_cuda_forward.cu:28-70).
-BC_HD BoxTaps taps_forward(float xmin, float xmax, float ymin, float ymax, bool normalize, bool exact)
+template <typename T>
+BC_HD BoxTapsT<T> taps_forward(T xmin, T xmax, T ymin, T ymax, bool normalize, bool exact)
 {
-    BoxTaps t;
-    float v;
-    v = ceilf(xmin);  t.lo_r = (int)v;      t.f_lo_r = v - xmin;
-    v = ceilf(ymin);  t.lo_c = (int)v;      t.f_lo_c = v - ymin;
-    v = floorf(xmax); t.hi_r = (int)v + 1;  t.f_hi_r = xmax - v;
-    v = floorf(ymax); t.hi_c = (int)v + 1;  t.f_hi_c = ymax - v;
-    if (!exact) t.f_lo_r = t.f_lo_c = t.f_hi_r = t.f_hi_c = 0.0f;
-    t.scale = normalize ? inv_area(xmin, xmax, ymin, ymax, exact, true, true) : 1.0f;
+    BoxTapsT<T> t;
+    T v;
+    v = bc_ceil(xmin);  t.lo_r = (int)v;      t.f_lo_r = v - xmin;
+    v = bc_ceil(ymin);  t.lo_c = (int)v;      t.f_lo_c = v - ymin;
+    v = bc_floor(xmax); t.hi_r = (int)v + 1;  t.f_hi_r = xmax - v;
+    v = bc_floor(ymax); t.hi_c = (int)v + 1;  t.f_hi_c = ymax - v;
+    if (!exact) t.f_lo_r = t.f_lo_c = t.f_hi_r = t.f_hi_c = T(0);
+    t.scale = normalize ? inv_area(xmin, xmax, ymin, ymax, exact, true, true) : T(1);
     return t;
 }
 
 // Split of the mirrored box [-max, -min] that grad-input gathers with over the integral image
 // of grad_output, src/box_convolution.cpp:43-69.
-BC_HD BoxTaps taps_mirrored(float xmin, float xmax, float ymin, float ymax, bool normalize, bool exact)
+template <typename T>
+BC_HD BoxTapsT<T> taps_mirrored(T xmin, T xmax, T ymin, T ymax, bool normalize, bool exact)
 {
-    BoxTaps t;
-    float v;
-    v = ceilf(-xmax);         t.lo_r = (int)v;  t.f_lo_r = v + xmax;
-    v = ceilf(-ymax);         t.lo_c = (int)v;  t.f_lo_c = v + ymax;
-    v = floorf(-xmin) + 1.0f; t.hi_r = (int)v;  t.f_hi_r = -xmin + 1.0f - v;
-    v = floorf(-ymin) + 1.0f; t.hi_c = (int)v;  t.f_hi_c = -ymin + 1.0f - v;
-    if (!exact) t.f_lo_r = t.f_lo_c = t.f_hi_r = t.f_hi_c = 0.0f;
-    t.scale = normalize ? inv_area(xmin, xmax, ymin, ymax, exact, true, true) : 1.0f;
+    BoxTapsT<T> t;
+    T v;
+    v = bc_ceil(-xmax);          t.lo_r = (int)v;  t.f_lo_r = v + xmax;
+    v = bc_ceil(-ymax);          t.lo_c = (int)v;  t.f_lo_c = v + ymax;
+    v = bc_floor(-xmin) + T(1);  t.hi_r = (int)v;  t.f_hi_r = -xmin + T(1) - v;
+    v = bc_floor(-ymin) + T(1);  t.hi_c = (int)v;  t.f_hi_c = -ymin + T(1) - v;
+    if (!exact) t.f_lo_r = t.f_lo_c = t.f_hi_r = t.f_hi_c = T(0);
+    t.scale = normalize ? inv_area(xmin, xmax, ymin, ymax, exact, true, true) : T(1);
     return t;
 }
 
@@ -84,7 +96,8 @@ struct StripCols {
     int hi[kStrip + 1];   // columns q0+hi_c   .. q0+hi_c+4, clamped to [0, w]
 };
 
-BC_HD StripCols strip_cols(const BoxTaps &t, int q0, int w)
+template <typename T>
+BC_HD StripCols strip_cols(const BoxTapsT<T> &t, int q0, int w)
 {
     StripCols s;
 #pragma unroll
@@ -98,38 +111,42 @@ BC_HD StripCols strip_cols(const BoxTaps &t, int q0, int w)
 // Column-combined value of one tap row for the 4 columns of a strip:
 //   D[c] = (1-f_hi) I[hi(c)] + f_hi I[hi(c)+1] - (1-f_lo) I[lo(c)] - f_lo I[lo(c)-1]
 // i.e. the fractional-width box sum of everything above that integral row.
-struct RowD {
-    float d[kStrip];
+template <typename T>
+struct RowDT {
+    T d[kStrip];
 };
+using RowD = RowDT<float>;
 
 // Same, plus the one-column strips just outside the box on either side (needed by the
 // parameter gradients): e_lo[c] = I[lo(c)] - I[lo(c)-1], e_hi[c] = I[hi(c)+1] - I[hi(c)].
-struct RowDE {
-    float d[kStrip], e_lo[kStrip], e_hi[kStrip];
+template <typename T>
+struct RowDET {
+    T d[kStrip], e_lo[kStrip], e_hi[kStrip];
 };
+using RowDE = RowDET<float>;
 
-template <class RowPtr>
-BC_HD RowD load_row_d(RowPtr row, const StripCols &s, const BoxTaps &t)
+template <typename T, class RowPtr>
+BC_HD RowDT<T> load_row_d(RowPtr row, const StripCols &s, const BoxTapsT<T> &t)
 {
-    float vl[kStrip + 1], vh[kStrip + 1];
+    T vl[kStrip + 1], vh[kStrip + 1];
 #pragma unroll
     for (int m = 0; m <= kStrip; ++m) { vl[m] = row[s.lo[m]]; vh[m] = row[s.hi[m]]; }
-    RowD r;
-    const float wh = 1.0f - t.f_hi_c, wl = 1.0f - t.f_lo_c;
+    RowDT<T> r;
+    const T wh = T(1) - t.f_hi_c, wl = T(1) - t.f_lo_c;
 #pragma unroll
     for (int c = 0; c < kStrip; ++c)
         r.d[c] = wh * vh[c] + t.f_hi_c * vh[c + 1] - wl * vl[c + 1] - t.f_lo_c * vl[c];
     return r;
 }
 
-template <class RowPtr>
-BC_HD RowDE load_row_de(RowPtr row, const StripCols &s, const BoxTaps &t)
+template <typename T, class RowPtr>
+BC_HD RowDET<T> load_row_de(RowPtr row, const StripCols &s, const BoxTapsT<T> &t)
 {
-    float vl[kStrip + 1], vh[kStrip + 1];
+    T vl[kStrip + 1], vh[kStrip + 1];
 #pragma unroll
     for (int m = 0; m <= kStrip; ++m) { vl[m] = row[s.lo[m]]; vh[m] = row[s.hi[m]]; }
-    RowDE r;
-    const float wh = 1.0f - t.f_hi_c, wl = 1.0f - t.f_lo_c;
+    RowDET<T> r;
+    const T wh = T(1) - t.f_hi_c, wl = T(1) - t.f_lo_c;
 #pragma unroll
     for (int c = 0; c < kStrip; ++c) {
         r.d[c] = wh * vh[c] + t.f_hi_c * vh[c + 1] - wl * vl[c + 1] - t.f_lo_c * vl[c];
@@ -141,7 +158,8 @@ BC_HD RowDE load_row_de(RowPtr row, const StripCols &s, const BoxTaps &t)
 
 // Row combination of the four tap rows {A = lo-1, B = lo, Cc = hi, Dd = hi+1}:
 //   (C - B) + f_hi (D - C) + f_lo (B - A)
-BC_HD float combine_rows(float a, float b, float c, float d, float f_lo, float f_hi)
+template <typename T>
+BC_HD T combine_rows(T a, T b, T c, T d, T f_lo, T f_hi)
 {
     return (c - b) + f_hi * (d - c) + f_lo * (b - a);
 }
@@ -154,21 +172,24 @@ BC_HD float combine_rows(float a, float b, float c, float d, float f_lo, float f
 //   s_left = sum X * (column strip outside the lo-column side)  -> d/d y_max
 //   s_right= sum X * (column strip outside the hi-column side)  -> d/d y_min
 // (the mirrored box's lo side is the original box's max side).
-struct ParamSums {
-    float s_out, s_top, s_bot, s_left, s_right;
+template <typename T>
+struct ParamSumsT {
+    T s_out, s_top, s_bot, s_left, s_right;
 };
+using ParamSums = ParamSumsT<float>;
 constexpr int kNumSums = 5;
 
 // Final parameter gradients from the five sums, src/box_convolution_interface.cpp:343-391:
 // integrand sums times 1/area, plus (when normalising) the derivative of 1/area times
 // sum(grad_output * output), times the reparametrization factor.
-BC_HD void finish_param_grads(const ParamSums &s, float xmin, float xmax, float ymin, float ymax,
-                              bool normalize, bool exact, float rep_h, float rep_w, float g[4])
+template <typename T>
+BC_HD void finish_param_grads(const ParamSumsT<T> &s, T xmin, T xmax, T ymin, T ymax,
+                              bool normalize, bool exact, T rep_h, T rep_w, T g[4])
 {
-    float ia = 1.0f, second_x = 0.0f, second_y = 0.0f;
+    T ia = T(1), second_x = T(0), second_y = T(0);
     if (normalize) {
         ia = inv_area(xmin, xmax, ymin, ymax, exact, true, true);
-        const float go_out = s.s_out * ia;   // sum(grad_output * output)
+        const T go_out = s.s_out * ia;   // sum(grad_output * output)
         second_x = go_out * inv_area(xmin, xmax, ymin, ymax, exact, true, false);
         second_y = go_out * inv_area(xmin, xmax, ymin, ymax, exact, false, true);
     }

@@ -831,7 +831,7 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     }
     st = check_launch("backward_plane");
     if (st != BC_OK || !need_params) return st;
-    return launch_finish_param_grads(partials, bp, C * F, N, normalize, exact, rep_h, rep_w, need_mask,
+    return launch_finish_param_grads<float>(partials, bp, C * F, N, normalize, exact, rep_h, rep_w, need_mask,
                                      grad_params, s);
 }
 

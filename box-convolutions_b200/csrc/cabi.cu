@@ -61,6 +61,97 @@ static inline size_t integral_bytes(int64_t planes, int h, int w)
     return align_up((size_t)planes * (size_t)(h + 1) * (size_t)(w + 1) * sizeof(float), 256);
 }
 
+
+
+// ---- the four extension functions, for float and double ------------------------------------
+template <typename T>
+static size_t integral_bytes_t(int64_t planes, int h, int w)
+{
+    return align_up((size_t)planes * (size_t)(h + 1) * (size_t)(w + 1) * sizeof(T), 256);
+}
+
+template <typename T>
+static int integral_image_entry(const T *in, T *out, int64_t planes, int h, int w, cudaStream_t stream)
+{
+    if (planes < 0 || h < 0 || w < 0 || h >= (1 << 24) || w >= (1 << 24)) return BC_ERR_BAD_SHAPE;
+    if (planes == 0) return BC_OK;
+    if (!out || (!in && h > 0 && w > 0)) return BC_ERR_NULL_POINTER;
+    return launch_integral_image<T>(in, out, planes, h, w, stream);
+}
+
+template <typename T>
+static int forward_entry(const T *input_integrated, const T *x_min, const T *x_max, const T *y_min,
+                         const T *y_max, T *output, int N, int C, int F, int h, int w, int normalize,
+                         int exact, cudaStream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (any_empty(N, C, F, h, w)) return BC_OK;
+    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
+    const BoxParamsT<T> bp{x_min, x_max, y_min, y_max, T(1), T(1)};
+    return launch_forward_global<T>(input_integrated, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+}
+
+template <typename T>
+static size_t backward_workspace_entry(int N, int C, int F, int h, int w, int need_mask)
+{
+    if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
+    return integral_bytes_t<T>((int64_t)N * C * F, h, w) +
+           align_up(backward_partials_bytes(N, C, F, h, w, sizeof(T)), 256);
+}
+
+template <typename T>
+static int backward_entry(const T *input_integrated, const T *x_min, const T *x_max, const T *y_min,
+                          const T *y_max, const T *grad_output, T reparametrization_h,
+                          T reparametrization_w, int N, int C, int F, int h, int w, int normalize,
+                          int exact, int need_mask, T *grad_input, T *grad_params, void *workspace,
+                          size_t workspace_bytes, cudaStream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    need_mask &= BC_NEED_ALL;
+    if (!need_mask) return BC_OK;
+    const bool need_params = (need_mask & ~BC_NEED_INPUT) != 0;
+    if (any_empty(N, C, F, h, w)) {
+        // nothing to gather; parameter gradients of an empty batch are zero
+        if (need_params && C > 0 && F > 0) {
+            if (!grad_params) return BC_ERR_NULL_POINTER;
+            for (int j = 0; j < 4; ++j)
+                if (need_mask & (BC_NEED_X_MIN << j))
+                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(T) * C * F, stream) != cudaSuccess)
+                        return check_launch("memset");
+        }
+        return BC_OK;
+    }
+    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !grad_output) return BC_ERR_NULL_POINTER;
+    if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
+    if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
+    const size_t ib = integral_bytes_t<T>((int64_t)N * C * F, h, w);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < backward_workspace_entry<T>(N, C, F, h, w, need_mask))
+        return BC_ERR_WORKSPACE;
+    T *go_integ = static_cast<T *>(workspace);
+    T *partials = reinterpret_cast<T *>(static_cast<char *>(workspace) + ib);
+
+    int st = launch_integral_image<T>(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
+    if (st != BC_OK) return st;
+    const BoxParamsT<T> bp{x_min, x_max, y_min, y_max, T(1), T(1)};
+    return launch_backward_global<T>(nullptr, input_integrated, go_integ, bp, reparametrization_h,
+                                     reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
+                                     need_mask, grad_input, grad_params, partials, stream);
+}
+
+template <typename T>
+static int clip_entry(T *x_min, T *x_max, T *y_min, T *y_max, int count, double reparametrization_h,
+                      double reparametrization_w, double max_input_h, double max_input_w, int exact,
+                      cudaStream_t stream)
+{
+    if (count < 0) return BC_ERR_BAD_SHAPE;
+    if (count == 0) return BC_OK;
+    if (!x_min || !x_max || !y_min || !y_max) return BC_ERR_NULL_POINTER;
+    if (reparametrization_h == 0.0 || reparametrization_w == 0.0) return BC_ERR_BAD_SHAPE;
+    return launch_clip<T>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
+                          max_input_h, max_input_w, exact != 0, stream);
+}
+
 }  // namespace bc
 
 using namespace bc;
@@ -86,10 +177,12 @@ const char *bc_last_cuda_error(void) { return g_last_error; }
 
 int bc_integral_image(const float *in, float *out, int64_t planes, int h, int w, bc_stream_t stream)
 {
-    if (planes < 0 || h < 0 || w < 0 || h >= (1 << 24) || w >= (1 << 24)) return BC_ERR_BAD_SHAPE;
-    if (planes == 0) return BC_OK;
-    if (!out || (!in && h > 0 && w > 0)) return BC_ERR_NULL_POINTER;
-    return launch_integral_image(in, out, planes, h, w, stream);
+    return integral_image_entry<float>(in, out, planes, h, w, stream);
+}
+
+int bc_integral_image_f64(const double *in, double *out, int64_t planes, int h, int w, bc_stream_t stream)
+{
+    return integral_image_entry<double>(in, out, planes, h, w, stream);
 }
 
 int bc_box_convolution_forward(const float *input_integrated, const float *x_min,
@@ -97,17 +190,27 @@ int bc_box_convolution_forward(const float *input_integrated, const float *x_min
                                float *output, int N, int C, int F, int h, int w, int normalize,
                                int exact, bc_stream_t stream)
 {
-    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
-    if (any_empty(N, C, F, h, w)) return BC_OK;
-    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
-    const BoxParams bp{x_min, x_max, y_min, y_max, 1.0f, 1.0f};
-    return launch_forward_global(input_integrated, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+    return forward_entry<float>(input_integrated, x_min, x_max, y_min, y_max, output, N, C, F, h, w,
+                                normalize, exact, stream);
+}
+
+int bc_box_convolution_forward_f64(const double *input_integrated, const double *x_min,
+                                   const double *x_max, const double *y_min, const double *y_max,
+                                   double *output, int N, int C, int F, int h, int w, int normalize,
+                                   int exact, bc_stream_t stream)
+{
+    return forward_entry<double>(input_integrated, x_min, x_max, y_min, y_max, output, N, C, F, h, w,
+                                 normalize, exact, stream);
 }
 
 size_t bc_box_convolution_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
 {
-    if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
-    return integral_bytes((int64_t)N * C * F, h, w) + align_up(backward_partials_bytes(N, C, F, h, w), 256);
+    return backward_workspace_entry<float>(N, C, F, h, w, need_mask);
+}
+
+size_t bc_box_convolution_backward_workspace_f64(int N, int C, int F, int h, int w, int need_mask)
+{
+    return backward_workspace_entry<double>(N, C, F, h, w, need_mask);
 }
 
 int bc_box_convolution_backward(const float *input_integrated, const float *x_min,
@@ -119,49 +222,41 @@ int bc_box_convolution_backward(const float *input_integrated, const float *x_mi
                                 void *workspace, size_t workspace_bytes, bc_stream_t stream)
 {
     (void)output;
-    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
-    need_mask &= BC_NEED_ALL;
-    if (!need_mask) return BC_OK;
-    const bool need_params = (need_mask & ~BC_NEED_INPUT) != 0;
-    if (any_empty(N, C, F, h, w)) {
-        // nothing to gather; parameter gradients of an empty batch are zero
-        if (need_params && C > 0 && F > 0) {
-            if (!grad_params) return BC_ERR_NULL_POINTER;
-            for (int j = 0; j < 4; ++j)
-                if (need_mask & (BC_NEED_X_MIN << j))
-                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream) != cudaSuccess)
-                        return check_launch("memset");
-        }
-        return BC_OK;
-    }
-    if (!input_integrated || !x_min || !x_max || !y_min || !y_max || !grad_output) return BC_ERR_NULL_POINTER;
-    if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
-    if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
-    const size_t ib = integral_bytes((int64_t)N * C * F, h, w);
-    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
-        workspace_bytes < bc_box_convolution_backward_workspace(N, C, F, h, w, need_mask))
-        return BC_ERR_WORKSPACE;
-    float *go_integ = static_cast<float *>(workspace);
-    float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
+    return backward_entry<float>(input_integrated, x_min, x_max, y_min, y_max, grad_output,
+                                 reparametrization_h, reparametrization_w, N, C, F, h, w, normalize,
+                                 exact, need_mask, grad_input, grad_params, workspace, workspace_bytes,
+                                 stream);
+}
 
-    int st = launch_integral_image(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
-    if (st != BC_OK) return st;
-    const BoxParams bp{x_min, x_max, y_min, y_max, 1.0f, 1.0f};
-    return launch_backward_global(nullptr, input_integrated, go_integ, bp, reparametrization_h,
-                                  reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
-                                  need_mask, grad_input, grad_params, partials, stream);
+int bc_box_convolution_backward_f64(const double *input_integrated, const double *x_min,
+                                    const double *x_max, const double *y_min, const double *y_max,
+                                    const double *grad_output, const double *output,
+                                    double reparametrization_h, double reparametrization_w, int N,
+                                    int C, int F, int h, int w, int normalize, int exact,
+                                    int need_mask, double *grad_input, double *grad_params,
+                                    void *workspace, size_t workspace_bytes, bc_stream_t stream)
+{
+    (void)output;
+    return backward_entry<double>(input_integrated, x_min, x_max, y_min, y_max, grad_output,
+                                  reparametrization_h, reparametrization_w, N, C, F, h, w, normalize,
+                                  exact, need_mask, grad_input, grad_params, workspace, workspace_bytes,
+                                  stream);
 }
 
 int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, int count,
                        double reparametrization_h, double reparametrization_w,
                        double max_input_h, double max_input_w, int exact, bc_stream_t stream)
 {
-    if (count < 0) return BC_ERR_BAD_SHAPE;
-    if (count == 0) return BC_OK;
-    if (!x_min || !x_max || !y_min || !y_max) return BC_ERR_NULL_POINTER;
-    if (reparametrization_h == 0.0 || reparametrization_w == 0.0) return BC_ERR_BAD_SHAPE;
-    return launch_clip(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
-                       max_input_h, max_input_w, exact != 0, stream);
+    return clip_entry<float>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
+                             max_input_h, max_input_w, exact, stream);
+}
+
+int bc_clip_parameters_f64(double *x_min, double *x_max, double *y_min, double *y_max, int count,
+                           double reparametrization_h, double reparametrization_w,
+                           double max_input_h, double max_input_w, int exact, bc_stream_t stream)
+{
+    return clip_entry<double>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
+                              max_input_h, max_input_w, exact, stream);
 }
 
 size_t bc_boxconv2d_forward_workspace(int N, int C, int F, int h, int w)
@@ -187,9 +282,9 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
         workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
         return BC_ERR_WORKSPACE;
     float *integ = static_cast<float *>(workspace);
-    int st = launch_integral_image(input, integ, (int64_t)N * C, h, w, stream);
+    int st = launch_integral_image<float>(input, integ, (int64_t)N * C, h, w, stream);
     if (st != BC_OK) return st;
-    return launch_forward_global(integ, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+    return launch_forward_global<float>(integ, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
 }
 
 size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
@@ -235,9 +330,9 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                                      grad_params, static_cast<float *>(workspace), stream);
     float *go_integ = static_cast<float *>(workspace);
     float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
-    int st = launch_integral_image(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
+    int st = launch_integral_image<float>(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
     if (st != BC_OK) return st;
-    return launch_backward_global(input, nullptr, go_integ, bp, reparametrization_h,
+    return launch_backward_global<float>(input, nullptr, go_integ, bp, reparametrization_h,
                                   reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
                                   need_mask, grad_input, grad_params, partials, stream);
 }

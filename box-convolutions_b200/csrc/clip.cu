@@ -9,21 +9,23 @@ namespace bc {
 
 namespace {
 
-__device__ __forceinline__ void clip_pair(float *pmin, float *pmax, double inv_rep, double min_size, double max_size)
+template <typename T>
+__device__ __forceinline__ void clip_pair(T *pmin, T *pmax, double inv_rep, double min_size, double max_size)
 {
     const double lo = -(max_size + 1) * inv_rep, hi = (max_size - 1) * inv_rep;
     double a = fmax(lo, fmin(hi, (double)*pmin));
     double b = fmax(lo, fmin(hi, (double)*pmax));
     if (a + (min_size - 0.9999) * inv_rep > b) {
-        const float mean = (float)(0.5 * (a + b));   // rounded to fp32, as the reference does
+        const T mean = (T)(0.5 * (a + b));   // rounded to the stored type, as the reference does
         a = mean - 0.5 * (min_size - 0.9999) * inv_rep;
         b = mean + 0.5 * (min_size - 0.9999) * inv_rep;
     }
-    *pmin = (float)a;
-    *pmax = (float)b;
+    *pmin = (T)a;
+    *pmax = (T)b;
 }
 
-__global__ void clip_kernel(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+template <typename T>
+__global__ void clip_kernel(T *x_min, T *x_max, T *y_min, T *y_max, int count,
                             double inv_rep_h, double inv_rep_w, double min_size, double max_h, double max_w)
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -36,7 +38,8 @@ __global__ void clip_kernel(float *x_min, float *x_max, float *y_min, float *y_m
 
 }  // namespace
 
-int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int count, double rep_h,
+template <typename T>
+int launch_clip(T *x_min, T *x_max, T *y_min, T *y_max, int count, double rep_h,
                 double rep_w, double max_h, double max_w, bool exact, cudaStream_t s)
 {
     if (count == 0) return BC_OK;
@@ -45,9 +48,12 @@ int launch_clip(float *x_min, float *x_max, float *y_min, float *y_max, int coun
     const int threads = 128;
     const int blocks = (2 * count + threads - 1) / threads;
     LaunchScope scope(KID_CLIP, s);
-    clip_kernel<<<blocks, threads, 0, s>>>(x_min, x_max, y_min, y_max, count, 1.0 / rep_h, 1.0 / rep_w,
+    clip_kernel<T><<<blocks, threads, 0, s>>>(x_min, x_max, y_min, y_max, count, 1.0 / rep_h, 1.0 / rep_w,
                                            min_size, max_h, max_w);
     return check_launch("clip_parameters");
 }
+
+template int launch_clip<float>(float *, float *, float *, float *, int, double, double, double, double, bool, cudaStream_t);
+template int launch_clip<double>(double *, double *, double *, double *, int, double, double, double, double, bool, cudaStream_t);
 
 }  // namespace bc

@@ -184,6 +184,60 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     }
 }
 
+// float64 planes (gradient checks, not a benchmarked path): the same three passes with scalar
+// 8-byte accesses, which are already full 256-byte requests per warp.
+__global__ void __launch_bounds__(kMaxThreads)
+integral_image_f64_kernel(const double *__restrict__ in, double *__restrict__ out, int h, int w, int tile_rows)
+{
+    extern __shared__ double tile64[];                         // tile_rows*(w+1) + w doubles
+    const int pw = w + 1;
+    double *carry = tile64 + tile_rows * pw;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kThreads = blockDim.x, kWarps = blockDim.x >> 5;
+    const int64_t plane = blockIdx.x;
+    const double *src = in + plane * (int64_t)h * w;
+    double *dst = out + plane * (int64_t)(h + 1) * pw;
+
+    for (int c = tid; c < w; c += kThreads) carry[c] = 0.0;
+    for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0;
+
+    for (int r0 = 0; r0 < h; r0 += tile_rows) {
+        const int rows = min(tile_rows, h - r0);
+        for (int i = warp; i < rows; i += kWarps) {
+            const double *row = src + (int64_t)(r0 + i) * w;
+            double *trow = tile64 + i * pw;
+            if (lane == 0) trow[0] = 0.0;
+            double running = 0.0;
+            for (int c0 = 0; c0 < w; c0 += 32) {
+                const int c = c0 + lane;
+                double v = c < w ? __ldg(row + c) : 0.0;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const double u = __shfl_up_sync(0xffffffffu, v, d);
+                    if (lane >= d) v += u;
+                }
+                if (c < w) trow[c + 1] = v + running;
+                running += __shfl_sync(0xffffffffu, v, 31);
+            }
+        }
+        __syncthreads();
+        for (int c = tid; c < w; c += kThreads) {
+            double run = carry[c];
+            double *col = tile64 + c + 1;
+            for (int i = 0; i < rows; ++i) {
+                run += col[i * pw];
+                col[i * pw] = run;
+            }
+            carry[c] = run;
+        }
+        __syncthreads();
+        double *gdst = dst + (int64_t)(r0 + 1) * pw;
+        const int n = rows * pw;
+        for (int s = tid; s < n; s += kThreads) gdst[s] = tile64[s];
+        __syncthreads();
+    }
+}
+
 }  // namespace
 
 // Shared memory a CTA needs for tiles of `tile_rows` rows.
@@ -192,7 +246,31 @@ static size_t tile_smem_bytes(int tile_rows, int w)
     return ((size_t)((tile_rows * (w + 1) + 4 + 3) & ~3) + (size_t)w) * sizeof(float);
 }
 
-int launch_integral_image(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
+template <>
+int launch_integral_image<double>(const double *in, double *out, int64_t planes, int h, int w, cudaStream_t s)
+{
+    if (planes == 0) return BC_OK;
+    if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
+    const int pw = w + 1;
+    int tile_rows = 4500 / pw;
+    if (tile_rows < 1) tile_rows = 1;
+    if (tile_rows > h) tile_rows = h > 0 ? h : 1;
+    const size_t smem = ((size_t)tile_rows * pw + (size_t)w) * sizeof(double);
+    if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(integral_image_f64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return check_launch("integral_image (f64): shared memory opt-in");
+    }
+    {
+        LaunchScope scope(KID_INTEGRAL, s);
+        integral_image_f64_kernel<<<(unsigned)planes, kMaxThreads, smem, s>>>(in, out, h, w, tile_rows);
+    }
+    return check_launch("integral_image (f64)");
+}
+
+template <>
+int launch_integral_image<float>(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
 {
     if (planes == 0) return BC_OK;
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;

@@ -99,6 +99,28 @@ int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, i
                        double reparametrization_h, double reparametrization_w,
                        double max_input_h, double max_input_w, int exact, bc_stream_t stream);
 
+/* ---- float64 forms of the four functions above ----------------------------------------
+ * The reference dispatches its operator over floating types (AT_DISPATCH_FLOATING_TYPES_AND_HALF,
+ * src/box_convolution_interface.cpp:51,201; src/integral_image_interface.cpp:8-27) and its own
+ * tests check gradients in float64 (test/test_boxconv.py).  Same arguments and behaviour as the
+ * float entry points, every array (workspace contents included) in double. */
+int bc_integral_image_f64(const double *in, double *out, int64_t planes, int h, int w, bc_stream_t stream);
+int bc_box_convolution_forward_f64(const double *input_integrated, const double *x_min,
+                                   const double *x_max, const double *y_min, const double *y_max,
+                                   double *output, int N, int C, int F, int h, int w, int normalize,
+                                   int exact, bc_stream_t stream);
+size_t bc_box_convolution_backward_workspace_f64(int N, int C, int F, int h, int w, int need_mask);
+int bc_box_convolution_backward_f64(const double *input_integrated, const double *x_min,
+                                    const double *x_max, const double *y_min, const double *y_max,
+                                    const double *grad_output, const double *output,
+                                    double reparametrization_h, double reparametrization_w, int N,
+                                    int C, int F, int h, int w, int normalize, int exact,
+                                    int need_mask, double *grad_input, double *grad_params,
+                                    void *workspace, size_t workspace_bytes, bc_stream_t stream);
+int bc_clip_parameters_f64(double *x_min, double *x_max, double *y_min, double *y_max, int count,
+                           double reparametrization_h, double reparametrization_w,
+                           double max_input_h, double max_input_w, int exact, bc_stream_t stream);
+
 /* ---- the module step, fused ------------------------------------------------------------
  * What BoxConvolutionFunction.forward / .backward do as a chain of extension calls
  * (box_convolution/box_convolution_function.py:32-65), taken from the input itself: the
