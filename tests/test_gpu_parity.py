@@ -336,6 +336,39 @@ def test_host_pipeline_matches_device_step(bc, cfg, batch, planes, chunks):
             assert max_rel(hgp[k].numpy(), gps[k]) < 1e-5, k
 
 
+def test_host_pipeline_batches_in_flight(bc):
+    """submit/wait with two batches in flight on alternating workspaces: five different batches
+    in a row, each compared with the module run on device tensors."""
+    base = make_workload("cfg2", batch=4, planes=5)
+    N, C, F, h, w = base.shape
+    rng = np.random.default_rng(77)
+    batches = [(rng.standard_normal(base.x.shape).astype(np.float32),
+                rng.standard_normal(base.grad_output.shape).astype(np.float32)) for _ in range(5)]
+    want = []
+    m = None
+    for x, go in batches:
+        out, gin, gps, m = run_module(bc, x, base.stored, go, base.max_h, base.max_w, 8, True, True)
+        want.append((out, gin, gps))
+    pipe = bc.HostPipeline(m, N, h, w, chunks=2, depth=2)
+    host_in = [(torch.from_numpy(x).pin_memory(), torch.from_numpy(go).pin_memory()) for x, go in batches]
+    host_out = [(torch.empty((N, C * F, h, w)).pin_memory(), torch.empty((N, C, h, w)).pin_memory(),
+                 torch.empty((4, C, F)).pin_memory()) for _ in batches]
+    tickets = []
+    for i, (hx, hgo) in enumerate(host_in):
+        if i >= 2:
+            pipe.wait(tickets[i - 2])
+        tickets.append(pipe.submit(hx, hgo, *host_out[i]))
+    with pytest.raises(RuntimeError):
+        pipe.submit(*host_in[0], *host_out[0])            # a third batch in flight is refused
+    for t in tickets:
+        pipe.wait(t)
+    for (hout, hgin, hgp), (out, gin, gps) in zip(host_out, want):
+        assert np.array_equal(hout.numpy(), out)
+        assert np.array_equal(hgin.numpy(), gin)
+        for k in range(4):
+            assert max_rel(hgp[k].numpy(), gps[k]) < 1e-5, k
+
+
 def test_no_bounded_wait_expired(bc):
     """Runs last in this file: the asynchronous plane copies of the staged kernels all completed."""
     from box_convolution import _cabi
