@@ -221,6 +221,7 @@ def kernel_algorithmic_bytes(kernel, N, C, F, h, w):
         "integral_image_kernel": None,     # depends on the plane count of the call; not the dominant kernel
         "forward_global_kernel": 4 * (Ei + F * E),
         "backward_global_kernel": 4 * (F * Ei + 2 * E),
+        "backward_band_kernel": 4 * (F * Ei + 2 * E),
         "forward_plane_kernel": 4 * E * (1 + F),
         "backward_plane_kernel": 4 * E * (F + 2),
     }.get(kernel)

@@ -41,7 +41,7 @@ int check_launch(const char *what);
 // Kernel ids reported by the profiling aid (bc_profile_get / bc_kernel_name).
 enum KernelId {
     KID_INTEGRAL = 1, KID_FORWARD_GLOBAL, KID_BACKWARD_GLOBAL, KID_FINISH_PARAM_GRADS, KID_CLIP,
-    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_COUNT
+    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_BACKWARD_BAND, KID_COUNT
 };
 
 // Put around a kernel launch: counts it and, while profiling is enabled, records a CUDA event on
@@ -94,6 +94,14 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
                           cudaStream_t s);
 
 int read_wait_timeouts(int *count);
+
+// Column-band backward for planes that do not fit in shared memory whole (box_band_smem.cu):
+// gathers from integral images in global memory, staged band by band.
+bool band_path_fits_backward(int F, int h, int w);
+size_t band_partials_bytes(int N, int C, int F, int w);
+int launch_backward_band(const float *x, const float *go_integ, const BoxParams &bp, float rep_h, float rep_w,
+                         int N, int C, int F, int h, int w, bool normalize, bool exact, int need_mask,
+                         float *grad_input, float *grad_params, float *partials, cudaStream_t s);
 
 
 }  // namespace bc

@@ -30,6 +30,7 @@
 // a multiple of 4 with 16-byte aligned tensors (no per-row guards, 128-bit global accesses), and
 // a guarded version for everything else.
 #include "bc_common.cuh"
+#include "bc_smem_walk.cuh"
 
 namespace bc {
 
@@ -44,67 +45,7 @@ constexpr int kMaxSmem = 200 * 1024;
 __host__ __device__ inline int layout_pitch(int w) { return w + 1 + 2 * kPad; }
 __host__ __device__ inline int layout_floats(int h, int w) { return (((h + 1) * layout_pitch(w) + (h >> 3) + 4) + 3) & ~3; }
 
-// Shared memory is addressed with 32-bit window addresses and explicit ld/st.shared so that the
-// five adjacent taps of a window cost one address computation and five immediate offsets.
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-template <int OFF>
-__device__ __forceinline__ float lds(uint32_t a)
-{
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(a), "n"(OFF));
-    return v;
-}
-template <int OFF>
-__device__ __forceinline__ void sts(uint32_t a, float v)
-{
-    asm volatile("st.shared.f32 [%0+%1], %2;" ::"r"(a), "n"(OFF), "f"(v));
-}
-__device__ __forceinline__ float4 lds128(uint32_t a)
-{
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-    return v;
-}
-// Two floats in one 64-bit register for the packed fp32 pipe of sm_100 (add/sub/mul/fma.f32x2):
-// one issue slot does the arithmetic of two lanes.  .x is the low half.
-typedef unsigned long long f2_t;
-__device__ __forceinline__ f2_t pack2(float lo, float hi)
-{
-    f2_t r;
-    asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f2_t v, float &lo, float &hi)
-{
-    asm("mov.b64 {%0,%1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f2_t fma2(f2_t a, f2_t b, f2_t c)
-{
-    f2_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ f2_t mul2(f2_t a, f2_t b)
-{
-    f2_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f2_t sub2(f2_t a, f2_t b)
-{
-    f2_t r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-
 inline int warp_tiles(int h, int w) { return ((w + kTile - 1) / kTile) * ((h + kTile - 1) / kTile); }
-
-__device__ __forceinline__ float warp_sum(float v)
-{
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-    return v;
-}
 
 struct Geometry {
     int h, w, col_tiles, row_tiles, ntiles, pitch4;
@@ -324,40 +265,6 @@ __device__ __forceinline__ void build_columns(Blocks<T> &b, const Strip (&st)[T]
     __syncthreads();
 }
 
-// Per-CTA table of the boxes this CTA works with (shared memory, filled once before the first
-// barrier): integer tap offsets, fractions and scale of BoxTaps, padded to three 16-byte words.
-constexpr int kMaxFilters = 32;
-constexpr int kTapWords = 12;
-
-__device__ __forceinline__ void store_taps(float *tab, const BoxTaps &t)
-{
-    int *ti = reinterpret_cast<int *>(tab);
-    ti[0] = t.lo_r; ti[1] = t.hi_r; ti[2] = t.lo_c; ti[3] = t.hi_c;
-    tab[4] = t.f_lo_r; tab[5] = t.f_hi_r; tab[6] = t.f_lo_c; tab[7] = t.f_hi_c;
-    tab[8] = t.scale; tab[9] = 0.f; tab[10] = 0.f; tab[11] = 0.f;
-}
-
-__device__ __forceinline__ BoxTaps load_taps(const float *tab)
-{
-    const float4 a = *reinterpret_cast<const float4 *>(tab);
-    const float4 b = *reinterpret_cast<const float4 *>(tab + 4);
-    BoxTaps t;
-    t.lo_r = __float_as_int(a.x); t.hi_r = __float_as_int(a.y);
-    t.lo_c = __float_as_int(a.z); t.hi_c = __float_as_int(a.w);
-    t.f_lo_r = b.x; t.f_hi_r = b.y; t.f_lo_c = b.z; t.f_hi_c = b.w;
-    t.scale = tab[8];
-    return t;
-}
-
-// Address arithmetic of a strip walk.  Tap rows are read in (lo, hi) pairs: the row on the lo
-// side of the box and the row on its hi side are fetched together and their values kept as the
-// two halves of packed registers, so the column combination runs on the f32x2 pipe.
-struct Walk {
-    uint32_t lo;      // address of the lo-side window (column clamp(q0+lo_c-1)) in row 0, no skew
-    uint32_t dhi;     // byte distance from the lo window to the hi window
-    int pitch4, h;
-};
-
 __device__ __forceinline__ Walk make_walk(uint32_t sI32, const BoxTaps &t, int q0, const Geometry &g)
 {
     const int bl = min(max(q0 + t.lo_c - 1, -kPad), g.w);
@@ -368,67 +275,6 @@ __device__ __forceinline__ Walk make_walk(uint32_t sI32, const BoxTaps &t, int q
     o.pitch4 = g.pitch4;
     o.h = g.h;
     return o;
-}
-
-__device__ __forceinline__ uint32_t tap_addr(const Walk &wk, int a)
-{
-    a = min(max(a, 0), wk.h);
-    return wk.lo + (uint32_t)(a * wk.pitch4) + (uint32_t)((a >> 3) << 2);
-}
-
-struct ColW2 {        // column weights of a box, each broadcast to both halves
-    f2_t wh, fh, nwl, nfl, fl;
-};
-
-__device__ __forceinline__ ColW2 col_weights(const BoxTaps &t)
-{
-    ColW2 c;
-    c.wh = pack2(1.0f - t.f_hi_c, 1.0f - t.f_hi_c);
-    c.fh = pack2(t.f_hi_c, t.f_hi_c);
-    c.nwl = pack2(t.f_lo_c - 1.0f, t.f_lo_c - 1.0f);
-    c.nfl = pack2(-t.f_lo_c, -t.f_lo_c);
-    c.fl = pack2(t.f_lo_c, t.f_lo_c);
-    return c;
-}
-
-// Column-combined values d[m] of the tap rows a_lo (low halves) and a_hi (high halves):
-//   d = (1-f_hi) h[m] + f_hi h[m+1] - (1-f_lo) l[m+1] - f_lo l[m]
-__device__ __forceinline__ void load_pair(const Walk &wk, int a_lo, int a_hi, const ColW2 &cw, f2_t d[kStrip])
-{
-    const uint32_t al0 = tap_addr(wk, a_lo), ah0 = al0 + wk.dhi;
-    const uint32_t al1 = tap_addr(wk, a_hi), ah1 = al1 + wk.dhi;
-    const f2_t l0 = pack2(lds<0>(al0), lds<0>(al1)), l1 = pack2(lds<4>(al0), lds<4>(al1));
-    const f2_t l2 = pack2(lds<8>(al0), lds<8>(al1)), l3 = pack2(lds<12>(al0), lds<12>(al1));
-    const f2_t l4 = pack2(lds<16>(al0), lds<16>(al1));
-    const f2_t h0 = pack2(lds<0>(ah0), lds<0>(ah1)), h1 = pack2(lds<4>(ah0), lds<4>(ah1));
-    const f2_t h2 = pack2(lds<8>(ah0), lds<8>(ah1)), h3 = pack2(lds<12>(ah0), lds<12>(ah1));
-    const f2_t h4 = pack2(lds<16>(ah0), lds<16>(ah1));
-    d[0] = fma2(cw.nfl, l0, fma2(cw.nwl, l1, fma2(cw.fh, h1, mul2(cw.wh, h0))));
-    d[1] = fma2(cw.nfl, l1, fma2(cw.nwl, l2, fma2(cw.fh, h2, mul2(cw.wh, h1))));
-    d[2] = fma2(cw.nfl, l2, fma2(cw.nwl, l3, fma2(cw.fh, h3, mul2(cw.wh, h2))));
-    d[3] = fma2(cw.nfl, l3, fma2(cw.nwl, l4, fma2(cw.fh, h4, mul2(cw.wh, h3))));
-}
-
-// Same plus the one-column strips outside the box: e_lo[m] = l[m+1]-l[m], e_hi[m] = h[m+1]-h[m],
-// and d = (h[m] - l[m+1]) + f_hi e_hi[m] + f_lo e_lo[m].
-__device__ __forceinline__ void load_pair_e(const Walk &wk, int a_lo, int a_hi, const ColW2 &cw, f2_t d[kStrip],
-                                            f2_t el[kStrip], f2_t eh[kStrip])
-{
-    const uint32_t al0 = tap_addr(wk, a_lo), ah0 = al0 + wk.dhi;
-    const uint32_t al1 = tap_addr(wk, a_hi), ah1 = al1 + wk.dhi;
-    f2_t l[kStrip + 1], hh[kStrip + 1];
-    l[0] = pack2(lds<0>(al0), lds<0>(al1)); l[1] = pack2(lds<4>(al0), lds<4>(al1));
-    l[2] = pack2(lds<8>(al0), lds<8>(al1)); l[3] = pack2(lds<12>(al0), lds<12>(al1));
-    l[4] = pack2(lds<16>(al0), lds<16>(al1));
-    hh[0] = pack2(lds<0>(ah0), lds<0>(ah1)); hh[1] = pack2(lds<4>(ah0), lds<4>(ah1));
-    hh[2] = pack2(lds<8>(ah0), lds<8>(ah1)); hh[3] = pack2(lds<12>(ah0), lds<12>(ah1));
-    hh[4] = pack2(lds<16>(ah0), lds<16>(ah1));
-#pragma unroll
-    for (int m = 0; m < kStrip; ++m) {
-        el[m] = sub2(l[m + 1], l[m]);
-        eh[m] = sub2(hh[m + 1], hh[m]);
-        d[m] = fma2(cw.fl, el[m], fma2(cw.fh, eh[m], sub2(hh[m], l[m + 1])));
-    }
 }
 
 template <int T, bool FAST>
@@ -516,7 +362,9 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
 // STAGED: the input plane and each grad_output plane arrive in shared memory by asynchronous bulk
 // copies (one instruction per plane, issued by one thread); the copy of the next grad_output
 // plane runs while the current one is gathered.
-template <int T, bool FAST, bool STAGED, bool NEED_PARAMS>
+// XSMEM: the input plane is kept in shared memory (else its values are read from global memory
+// as they are needed, which lets planes of up to ~48 000 pixels use this kernel).
+template <int T, bool FAST, bool STAGED, bool NEED_PARAMS, bool XSMEM = true>
 __global__ void __launch_bounds__(512)
 backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ grad_output, BoxParams bp,
                       float *__restrict__ grad_input, float *__restrict__ partials, int N, int C, int F,
@@ -529,7 +377,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     float *sRow = sI + layout_floats(h, w);
     float *sCol = sRow + g.ntiles * kTile;
     float *sX = sCol + g.ntiles * kTile;                   // the input plane, pitch w (NEED_PARAMS)
-    float *sG = sX + (NEED_PARAMS ? npix : 0);             // staged grad_output plane (STAGED)
+    float *sG = sX + (NEED_PARAMS && XSMEM ? npix : 0);    // staged grad_output plane (STAGED)
     __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
     __shared__ float red[16][kNumSums];
     __shared__ __align__(8) unsigned long long mbar[2];
@@ -564,7 +412,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
             bulk_load(sG32, gbase, plane_bytes, mbarG);
             if (NEED_PARAMS) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
         }
-    } else if (NEED_PARAMS) {
+    } else if (NEED_PARAMS && XSMEM) {
         const float *xp = x + nc * (int64_t)npix;
         if (FAST) {
             for (int i = tid; i < (npix >> 2); i += blockDim.x)
@@ -620,6 +468,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
                     f2_t pd[kStrip], pel[kStrip], peh[kStrip];
                     load_pair_e(wk, st[k].p0 + t.lo_r - 1, st[k].p0 + t.hi_r, cw, pd, pel, peh);
                     uint32_t xa = sX32 + st[k].pix * 4;
+                    const float *xg = x + nc * (int64_t)npix + st[k].pix;      // used when !XSMEM
 #pragma unroll
                     for (int i = 0; i < kR; ++i) {
                         const int p = st[k].p0 + i;
@@ -628,13 +477,15 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
                             load_pair_e(wk, p + t.lo_r, p + t.hi_r + 1, cw, cd, cel, ceh);
                             float xv[kStrip];
                             if (FAST) {
-                                const float4 v = lds128(xa);
+                                const float4 v = XSMEM ? lds128(xa) : __ldg(reinterpret_cast<const float4 *>(xg));
                                 xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
                             } else {
 #pragma unroll
-                                for (int m = 0; m < kStrip; ++m) xv[m] = st[k].q0 + m < w ? sX[p * w + st[k].q0 + m] : 0.0f;
+                                for (int m = 0; m < kStrip; ++m)
+                                    xv[m] = st[k].q0 + m < w ? (XSMEM ? sX[p * w + st[k].q0 + m] : __ldg(xg + m)) : 0.0f;
                             }
                             xa += w * 4;
+                            xg += w;
 #pragma unroll
                             for (int m = 0; m < kStrip; ++m) {
                                 const f2_t xx = pack2(xv[m], xv[m]);
@@ -761,7 +612,7 @@ bool plane_path_fits_forward(int F, int h, int w)
 
 bool plane_path_fits_backward(int F, int h, int w)
 {
-    return F <= kMaxFilters && warp_tiles(h, w) <= kMaxTiles && backward_smem_bytes(h, w, true, false) <= kMaxSmem;
+    return F <= kMaxFilters && warp_tiles(h, w) <= kMaxTiles && backward_smem_bytes(h, w, false, false) <= kMaxSmem;
 }
 
 int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
@@ -807,13 +658,18 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
                       (!write_gin || aligned16(grad_input));
     // bulk copies need 16-byte aligned planes of a multiple of 16 bytes (implied by `fast`) and room
     // for the staging buffer; staging must not cost a resident CTA (two fit below ~112 KB each)
+    // the input plane joins the integral image in shared memory when both fit
+    const bool xsmem = !need_params || backward_smem_bytes(h, w, true, false) <= kMaxSmem;
     const size_t with_staging = backward_smem_bytes(h, w, need_params, true);
     const size_t two_ctas = 112 * 1024;
-    const bool staged = fast && T == 1 && with_staging <= kMaxSmem &&
+    const bool staged = fast && T == 1 && xsmem && with_staging <= kMaxSmem &&
                         (with_staging <= two_ctas || backward_smem_bytes(h, w, need_params, false) > two_ctas);
-    const size_t smem = backward_smem_bytes(h, w, need_params, staged);
+    const size_t smem = backward_smem_bytes(h, w, need_params && xsmem, staged);
     void (*kern)(const float *, const float *, BoxParams, float *, float *, int, int, int, int, int, bool, bool, bool);
-    if (staged) {
+    if (!xsmem) {
+        if (fast) kern = T == 1 ? backward_plane_kernel<1, true, false, true, false> : backward_plane_kernel<2, true, false, true, false>;
+        else kern = T == 1 ? backward_plane_kernel<1, false, false, true, false> : backward_plane_kernel<2, false, false, true, false>;
+    } else if (staged) {
         kern = need_params ? backward_plane_kernel<1, true, true, true> : backward_plane_kernel<1, true, true, false>;
     } else if (fast) {
         kern = T == 1 ? (need_params ? backward_plane_kernel<1, true, false, true> : backward_plane_kernel<1, true, false, false>)

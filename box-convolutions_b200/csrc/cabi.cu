@@ -292,7 +292,10 @@ size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int ne
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
     if (plane_path_fits_backward(F, h, w))
         return align_up((size_t)C * F * N * kNumSums * sizeof(float), 256);
-    return bc_box_convolution_backward_workspace(N, C, F, h, w, need_mask);
+    size_t partials = backward_partials_bytes(N, C, F, h, w);
+    if (band_path_fits_backward(F, h, w) && band_partials_bytes(N, C, F, w) > partials)
+        partials = band_partials_bytes(N, C, F, w);
+    return integral_bytes((int64_t)N * C * F, h, w) + align_up(partials, 256);
 }
 
 int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x_max,
@@ -332,6 +335,9 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
     float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
     int st = launch_integral_image<float>(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
     if (st != BC_OK) return st;
+    if (band_path_fits_backward(F, h, w))
+        return launch_backward_band(input, go_integ, bp, reparametrization_h, reparametrization_w, N, C, F, h, w,
+                                    normalize != 0, exact != 0, need_mask, grad_input, grad_params, partials, stream);
     return launch_backward_global<float>(input, nullptr, go_integ, bp, reparametrization_h,
                                   reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
                                   need_mask, grad_input, grad_params, partials, stream);
@@ -445,6 +451,7 @@ const char *bc_kernel_name(int kernel_id)
         case KID_FORWARD_PLANE: return "forward_plane_kernel";
         case KID_BACKWARD_PLANE: return "backward_plane_kernel";
         case KID_SUM_CHUNKS: return "sum_chunk_grads_kernel";
+        case KID_BACKWARD_BAND: return "backward_band_kernel";
         default: return "unknown";
     }
 }

@@ -178,7 +178,12 @@ def test_module_cfg3_subset_vs_oracle(bc):
 @pytest.mark.parametrize("normalize,exact", [(True, True), (False, True), (True, False), (False, False)])
 @pytest.mark.parametrize("shape", [(2, 3, 2, 9, 11), (1, 2, 4, 33, 70), (3, 1, 1, 1, 1), (1, 5, 3, 64, 4),
                                    (2, 2, 3, 40, 131), (1, 2, 2, 128, 128), (1, 1, 2, 96, 200),
-                                   (1, 1, 1, 200, 300)])
+                                   (1, 1, 1, 200, 300),
+                                   # whole-plane backward with the input read from global memory
+                                   (1, 2, 2, 128, 256), (1, 1, 2, 125, 250),
+                                   # planes beyond the whole-plane kernels: column bands (guarded and
+                                   # unguarded), bands forward with the general backward, general both
+                                   (1, 2, 2, 203, 301), (2, 1, 3, 264, 96), (1, 1, 2, 600, 20), (1, 1, 1, 1100, 12)])
 def test_module_random_shapes_vs_oracle(bc, shape, normalize, exact):
     N, C, F, h, w = shape
     rng = np.random.default_rng(h * 1000 + w + 7 * int(normalize) + 13 * int(exact))
