@@ -5,7 +5,8 @@ from .function import BoxConvolutionFunction, reparametrize
 from .ext import integral_image, box_convolution_forward, box_convolution_backward, clip_parameters
 from .distributed import allreduce_box_gradients, packed_box_gradient
 from .host import HostPipeline
+from .inference import fused_box_block, fold_batchnorm, GraphedForward
 
-__all__ = ["BoxConv2d", "BoxConvolutionFunction", "reparametrize", "integral_image",
+__all__ = ["fused_box_block", "fold_batchnorm", "GraphedForward", "BoxConv2d", "BoxConvolutionFunction", "reparametrize", "integral_image",
            "box_convolution_forward", "box_convolution_backward", "clip_parameters",
            "allreduce_box_gradients", "packed_box_gradient", "HostPipeline"]

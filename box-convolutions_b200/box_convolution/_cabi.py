@@ -35,6 +35,7 @@ SIGNATURES = {
     "bc_clip_parameters_f64": (_i, [_vp] * 4 + [_i, _d, _d, _d, _d, _i, _vp]),
     "bc_boxconv2d_forward_workspace": (_sz, [_i] * 5),
     "bc_boxconv2d_forward": (_i, [_vp] * 5 + [_f, _f, _vp] + [_i] * 7 + [_vp, _sz, _vp]),
+    "bc_boxconv2d_forward_fused": (_i, [_vp] * 5 + [_f, _f, _vp] + [_i] * 8 + [_vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "bc_boxconv2d_backward_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_backward": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_boxconv2d_backward_static": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp]),

@@ -35,6 +35,15 @@ __device__ __forceinline__ BoxT<T> load_box(const BoxParamsT<T> &p, int k)
     return b;
 }
 
+// What the fused inference forward does around the gather (all optional): ReLU on the input as
+// it is read, then per output channel k = c*F + f:  out = act(scale[k] * box(x) + shift[k] + residual).
+struct Fusion {
+    int input_relu;
+    const float *scale, *shift;     // (C*F) each, or null for 1 / 0
+    const float *residual;          // (N, C*F, h, w) or null; may be the output buffer itself
+    int output_relu;
+};
+
 // Records a CUDA launch error for bc_last_cuda_error() and maps it to a status code.
 int check_launch(const char *what);
 
@@ -81,6 +90,15 @@ template <typename T>
 int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int count, int per_box,
                               bool normalize, bool exact, T rep_h, T rep_w, int need_mask,
                               T *grad_params, cudaStream_t s);
+
+// float integral image with an optional ReLU on the values read
+int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h, int w, bool relu_in,
+                              cudaStream_t s);
+// forward with the Fusion steps; a null `fu` is the plain forward
+int launch_forward_global_fused(const float *integ, const BoxParams &bp, const Fusion &fu, float *out, int N,
+                                int C, int F, int h, int w, bool normalize, bool exact, cudaStream_t s);
+int launch_forward_plane_fused(const float *x, const BoxParams &bp, const Fusion &fu, float *out, int N, int C,
+                               int F, int h, int w, bool normalize, bool exact, cudaStream_t s);
 
 // Shared-memory-resident path for small planes (box_plane_smem.cu).
 bool plane_path_fits_forward(int F, int h, int w);

@@ -78,6 +78,47 @@ forward_global_kernel(const T *__restrict__ integ, BoxParamsT<T> bp, T *__restri
     });
 }
 
+// Forward with the inference steps around the gather (float): the input ReLU has already gone
+// into the integral image; here the per-channel affine, the residual and the output ReLU.
+__global__ void __launch_bounds__(kThreads)
+forward_global_fused_kernel(const float *__restrict__ integ, BoxParams bp, Fusion fu, float *out,
+                            int C, int F, int h, int w, int row_tiles, int col_tiles, bool normalize, bool exact)
+{
+    int64_t b = blockIdx.x;
+    const int ct = (int)(b % col_tiles); b /= col_tiles;
+    const int rt = (int)(b % row_tiles); b /= row_tiles;
+    const int f = (int)(b % F);
+    const int64_t nc = b / F;
+    const int c = (int)(nc % C);
+
+    const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+    const int q0 = ct * kTileCols + lane * kStrip;
+    const int p0 = rt * kTileRows + rg * kRowsPerThread;
+    if (q0 >= w || p0 >= h) return;
+    const int p1 = min(p0 + kRowsPerThread, h);
+
+    const Box box = load_box(bp, c * F + f);
+    const BoxTaps t = taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact);
+    const StripCols sc = strip_cols(t, q0, w);
+    const GlobalRows<float> rows{integ + nc * (int64_t)(h + 1) * (w + 1), w + 1};
+    const int64_t plane = (nc * F + f) * (int64_t)h * w;
+    const float mul = fu.scale ? __ldg(fu.scale + c * F + f) : 1.0f;
+    const float add = fu.shift ? __ldg(fu.shift + c * F + f) : 0.0f;
+    const bool vec = (w % kStrip == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+
+    walk_forward(rows, t, sc, p0, p1, h, [&](int p, const float *v) {
+        const int64_t off = plane + (int64_t)p * w + q0;
+        float r[kStrip];
+#pragma unroll
+        for (int m = 0; m < kStrip; ++m) {
+            r[m] = v[m] * mul + add;
+            if (fu.residual && q0 + m < w) r[m] += fu.residual[off + m];   // plain load: may alias `out`
+            if (fu.output_relu) r[m] = fmaxf(r[m], 0.0f);
+        }
+        store_strip(out + off, r, q0, w, vec);
+    });
+}
+
 template <typename T>
 __device__ __forceinline__ T warp_sum(T v)
 {
@@ -280,6 +321,21 @@ int launch_forward_global(const T *integ, const BoxParamsT<T> &bp, T *out, int N
                                                                         col_tiles, normalize, exact);
     }
     return check_launch("forward_global");
+}
+
+int launch_forward_global_fused(const float *integ, const BoxParams &bp, const Fusion &fu, float *out, int N,
+                                int C, int F, int h, int w, bool normalize, bool exact, cudaStream_t s)
+{
+    const int row_tiles = ceil_div(h, kTileRows), col_tiles = ceil_div(w, kTileCols);
+    const int64_t blocks = (int64_t)N * C * F * row_tiles * col_tiles;
+    if (blocks == 0) return BC_OK;
+    if (blocks > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
+    {
+        LaunchScope scope(KID_FORWARD_GLOBAL, s);
+        forward_global_fused_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(integ, bp, fu, out, C, F, h, w, row_tiles,
+                                                                         col_tiles, normalize, exact);
+    }
+    return check_launch("forward_global (fused)");
 }
 
 size_t backward_partials_bytes(int N, int C, int F, int h, int w, size_t elem_size)

@@ -140,9 +140,10 @@ struct Blocks {
 // memory when STAGED, else from global memory), prefix it along rows inside the thread and across
 // the 8 column-group lanes, publish the tile's row totals.  Ends with a barrier, after which the
 // staged plane is no longer needed.
-template <int T, bool FAST, bool STAGED>
+template <int T, bool FAST, bool STAGED, bool MAYBE_RELU = false>
 __device__ __forceinline__ void build_rows(Blocks<T> &b, const Strip (&st)[T], const float *__restrict__ src,
-                                           uint32_t sG32, float *sRow, const Geometry &g, int cg, int rg)
+                                           uint32_t sG32, float *sRow, const Geometry &g, int cg, int rg,
+                                           bool relu = false)
 {
 #pragma unroll
     for (int k = 0; k < T; ++k) {
@@ -162,6 +163,14 @@ __device__ __forceinline__ void build_rows(Blocks<T> &b, const Strip (&st)[T], c
                     b.v[k][i][m] = (in && st[k].q0 + m < g.w) ? __ldg(src + st[k].pix + i * g.w + m) : 0.0f;
             }
         }
+    }
+    if (MAYBE_RELU && relu) {
+#pragma unroll
+        for (int k = 0; k < T; ++k)
+#pragma unroll
+            for (int i = 0; i < kR; ++i)
+#pragma unroll
+                for (int m = 0; m < kStrip; ++m) b.v[k][i][m] = fmaxf(b.v[k][i][m], 0.0f);
     }
 #pragma unroll
     for (int k = 0; k < T; ++k) {
@@ -277,10 +286,12 @@ __device__ __forceinline__ Walk make_walk(uint32_t sI32, const BoxTaps &t, int q
     return o;
 }
 
-template <int T, bool FAST>
+// FUSED: the inference steps of `Fusion` around the gather (the output may then alias the residual,
+// so it is not declared restrict).
+template <int T, bool FAST, bool FUSED = false>
 __global__ void __launch_bounds__(256, T == 1 ? 4 : 1)
-forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restrict__ out, int C, int F,
-                     int h, int w, int fsplit, bool normalize, bool exact)
+forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *out, int C, int F,
+                     int h, int w, int fsplit, bool normalize, bool exact, Fusion fu)
 {
     extern __shared__ float4 smem4[];
     float *sI = reinterpret_cast<float *>(smem4);
@@ -309,7 +320,7 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
     init_integral_padding(sI, g);
     {
         Blocks<T> blk;
-        build_rows<T, FAST, false>(blk, st, x + nc * (int64_t)h * w, 0u, sRow, g, cg, rg);
+        build_rows<T, FAST, false, FUSED>(blk, st, x + nc * (int64_t)h * w, 0u, sRow, g, cg, rg, FUSED && fu.input_relu);
         build_columns<T, FAST>(blk, st, sRow, sCol, g, cg, rg);
     }
 
@@ -318,6 +329,11 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
         const ColW2 cw = col_weights(t);
         const float sfl = t.scale * t.f_lo_r, sfh = t.scale * t.f_hi_r;
         float *o = out + (nc * F + f) * (int64_t)h * w;
+        float mul = 1.0f, add = 0.0f;
+        if (FUSED) {
+            if (fu.scale) mul = __ldg(fu.scale + c * F + f);
+            if (fu.shift) add = __ldg(fu.shift + c * F + f);
+        }
 #pragma unroll
         for (int k = 0; k < T; ++k) {
             if (!st[k].active) continue;
@@ -325,6 +341,7 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
             f2_t prev[kStrip];                 // (d of row lo-1, d of row hi) of the current pixel row
             load_pair(wk, st[k].p0 + t.lo_r - 1, st[k].p0 + t.hi_r, cw, prev);
             float *dst = o + st[k].pix;
+            const float *res = (FUSED && fu.residual) ? fu.residual + (nc * F + f) * (int64_t)h * w + st[k].pix : nullptr;
 #pragma unroll
             for (int i = 0; i < kR; ++i) {
                 const int p = st[k].p0 + i;
@@ -342,6 +359,25 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *__restric
                         v[m] = (cc - b) * t.scale + sfh * bot + sfl * top;
                         (void)a; (void)dd;
                         prev[m] = cur[m];
+                    }
+                    if (FUSED) {
+#pragma unroll
+                        for (int m = 0; m < kStrip; ++m) v[m] = v[m] * mul + add;
+                        if (res) {
+                            if (FAST) {
+                                const float4 r = *reinterpret_cast<const float4 *>(res);
+                                v[0] += r.x; v[1] += r.y; v[2] += r.z; v[3] += r.w;
+                            } else {
+#pragma unroll
+                                for (int m = 0; m < kStrip; ++m)
+                                    if (st[k].q0 + m < w) v[m] += res[m];
+                            }
+                            res += w;
+                        }
+                        if (fu.output_relu) {
+#pragma unroll
+                            for (int m = 0; m < kStrip; ++m) v[m] = fmaxf(v[m], 0.0f);
+                        }
                     }
                     if (FAST) {
                         *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -615,8 +651,8 @@ bool plane_path_fits_backward(int F, int h, int w)
     return F <= kMaxFilters && warp_tiles(h, w) <= kMaxTiles && backward_smem_bytes(h, w, false, false) <= kMaxSmem;
 }
 
-int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
-                         int w, bool normalize, bool exact, cudaStream_t s)
+static int launch_forward_plane_impl(const float *x, const BoxParams &bp, const Fusion *fu, float *out, int N,
+                                     int C, int F, int h, int w, bool normalize, bool exact, cudaStream_t s)
 {
     const int64_t planes = (int64_t)N * C;
     // Split the filters of a plane over two CTAs when there are too few planes to balance 148 SMs
@@ -629,17 +665,37 @@ int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N,
     const int tiles = warp_tiles(h, w);
     const int T = tiles > 16 ? 4 : (tiles > 8 ? 2 : 1);
     const int warps = (tiles + T - 1) / T;
-    const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(out);
-    void (*kern)(const float *, BoxParams, float *, int, int, int, int, int, bool, bool);
-    if (fast) kern = T == 1 ? forward_plane_kernel<1, true> : (T == 2 ? forward_plane_kernel<2, true> : forward_plane_kernel<4, true>);
-    else kern = T == 1 ? forward_plane_kernel<1, false> : (T == 2 ? forward_plane_kernel<2, false> : forward_plane_kernel<4, false>);
+    const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(out) &&
+                      (!fu || !fu->residual || aligned16(fu->residual));
+    void (*kern)(const float *, BoxParams, float *, int, int, int, int, int, bool, bool, Fusion);
+    if (fu) {
+        if (fast) kern = T == 1 ? forward_plane_kernel<1, true, true> : (T == 2 ? forward_plane_kernel<2, true, true> : forward_plane_kernel<4, true, true>);
+        else kern = T == 1 ? forward_plane_kernel<1, false, true> : (T == 2 ? forward_plane_kernel<2, false, true> : forward_plane_kernel<4, false, true>);
+    } else {
+        if (fast) kern = T == 1 ? forward_plane_kernel<1, true> : (T == 2 ? forward_plane_kernel<2, true> : forward_plane_kernel<4, true>);
+        else kern = T == 1 ? forward_plane_kernel<1, false> : (T == 2 ? forward_plane_kernel<2, false> : forward_plane_kernel<4, false>);
+    }
     int st = opt_in_smem(kern, smem);
     if (st != BC_OK) return st;
+    const Fusion none{0, nullptr, nullptr, nullptr, 0};
     {
         LaunchScope scope(KID_FORWARD_PLANE, s);
-        kern<<<(unsigned)(planes * fsplit), warps * 32, smem, s>>>(x, bp, out, C, F, h, w, fsplit, normalize, exact);
+        kern<<<(unsigned)(planes * fsplit), warps * 32, smem, s>>>(x, bp, out, C, F, h, w, fsplit, normalize, exact,
+                                                                  fu ? *fu : none);
     }
     return check_launch("forward_plane");
+}
+
+int launch_forward_plane(const float *x, const BoxParams &bp, float *out, int N, int C, int F, int h,
+                         int w, bool normalize, bool exact, cudaStream_t s)
+{
+    return launch_forward_plane_impl(x, bp, nullptr, out, N, C, F, h, w, normalize, exact, s);
+}
+
+int launch_forward_plane_fused(const float *x, const BoxParams &bp, const Fusion &fu, float *out, int N, int C,
+                               int F, int h, int w, bool normalize, bool exact, cudaStream_t s)
+{
+    return launch_forward_plane_impl(x, bp, &fu, out, N, C, F, h, w, normalize, exact, s);
 }
 
 int launch_backward_plane(const float *x, const float *grad_output, const BoxParams &bp, float rep_h,

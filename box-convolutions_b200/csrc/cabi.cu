@@ -287,6 +287,29 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
     return launch_forward_global<float>(integ, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
 }
 
+int bc_boxconv2d_forward_fused(const float *input, const float *x_min, const float *x_max,
+                               const float *y_min, const float *y_max, float reparametrization_h,
+                               float reparametrization_w, float *output, int N, int C, int F, int h,
+                               int w, int normalize, int exact, int input_relu, const float *out_scale,
+                               const float *out_shift, const float *residual, int output_relu,
+                               void *workspace, size_t workspace_bytes, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (any_empty(N, C, F, h, w)) return BC_OK;
+    if (!input || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
+    const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
+    const Fusion fu{input_relu != 0, out_scale, out_shift, residual, output_relu != 0};
+    if (plane_path_fits_forward(F, h, w))
+        return launch_forward_plane_fused(input, bp, fu, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
+        return BC_ERR_WORKSPACE;
+    float *integ = static_cast<float *>(workspace);
+    int st = launch_integral_image_f32(input, integ, (int64_t)N * C, h, w, input_relu != 0, stream);
+    if (st != BC_OK) return st;
+    return launch_forward_global_fused(integ, bp, fu, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+}
+
 size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
 {
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;

@@ -34,12 +34,18 @@ __device__ __forceinline__ float warp_inclusive_scan(float v, int lane)
 constexpr int kBatch = 8;      // 128-bit loads a lane keeps in flight: 8 x 32 lanes x 16 B = one 1024-float row
 
 // Loads kBatch consecutive 128-column segments of a row, starting at segment seg0.
-__device__ __forceinline__ void load_segments(const float4 *row4, int n4, int seg0, int lane, float4 (&buf)[kBatch])
+__device__ __forceinline__ float4 relu4(float4 v)
+{
+    return make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
+}
+
+__device__ __forceinline__ void load_segments(const float4 *row4, int n4, int seg0, int lane, float4 (&buf)[kBatch], bool relu)
 {
 #pragma unroll
     for (int k = 0; k < kBatch; ++k) {
         const int j = (seg0 + k) * 32 + lane;
         buf[k] = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (relu) buf[k] = relu4(buf[k]);
     }
 }
 
@@ -71,7 +77,7 @@ __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n
 // planes) the kernel stays small in registers and relies on many resident CTAs.
 template <bool VEC4, bool PIPELINED>
 __global__ void __launch_bounds__(kMaxThreads)
-integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int h, int w, int tile_rows)
+integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int h, int w, int tile_rows, bool relu)
 {
     extern __shared__ float4 smem4[];
     float *tile = reinterpret_cast<float *>(smem4);           // tile_rows*(w+1) + 4 floats
@@ -86,7 +92,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     const int n4 = w >> 2;
     float4 pre[kBatch];      // dead in the instantiations that are not PIPELINED
     if (PIPELINED && warp < tile_rows && warp < h)
-        load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre);
+        load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre, relu);
 
     for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
     for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
@@ -107,7 +113,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
             }
             const int rn = r0 + tile_rows + warp;
             if (warp < tile_rows && rn < h)
-                load_segments(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, 0, lane, pre);
+                load_segments(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, 0, lane, pre, relu);
         } else {
             for (int i = warp; i < rows; i += kWarps) {
                 const float *row = src + (int64_t)(r0 + i) * w;
@@ -118,7 +124,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
                     const float4 *row4 = reinterpret_cast<const float4 *>(row);
                     float4 nxt = lane < n4 ? __ldg(row4 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int c4 = 0; c4 < n4; c4 += 32) {
-                        float4 v = nxt;
+                        float4 v = relu ? relu4(nxt) : nxt;
                         const int j = c4 + 32 + lane;
                         if (c4 + 32 < n4) nxt = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
                         v.y += v.x; v.z += v.y; v.w += v.z;
@@ -134,7 +140,8 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
                 } else {
                     for (int c0 = 0; c0 < w; c0 += 32) {
                         const int c = c0 + lane;
-                        const float v = c < w ? __ldg(row + c) : 0.0f;
+                        float v = c < w ? __ldg(row + c) : 0.0f;
+                        if (relu) v = fmaxf(v, 0.0f);
                         const float incl = warp_inclusive_scan(v, lane);
                         if (c < w) trow[c + 1] = incl + running;
                         running += __shfl_sync(0xffffffffu, incl, 31);
@@ -272,6 +279,11 @@ int launch_integral_image<double>(const double *in, double *out, int64_t planes,
 template <>
 int launch_integral_image<float>(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
 {
+    return launch_integral_image_f32(in, out, planes, h, w, false, s);
+}
+
+int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h, int w, bool relu_in, cudaStream_t s)
+{
     if (planes == 0) return BC_OK;
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const int pw = w + 1;
@@ -284,7 +296,7 @@ int launch_integral_image<float>(const float *in, float *out, int64_t planes, in
     if (tile_rows > h) tile_rows = h > 0 ? h : 1;
     const size_t smem = tile_smem_bytes(tile_rows, w);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
-    void (*kern)(const float *, float *, int, int, int) =
+    void (*kern)(const float *, float *, int, int, int, bool) =
         pipelined ? integral_image_kernel<true, true>
                   : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
     if (smem > 48 * 1024) {
@@ -293,7 +305,7 @@ int launch_integral_image<float>(const float *in, float *out, int64_t planes, in
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
-        kern<<<(unsigned)planes, kMaxThreads, smem, s>>>(in, out, h, w, tile_rows);
+        kern<<<(unsigned)planes, kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in);
     }
     return check_launch("integral_image");
 }

@@ -134,6 +134,24 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
                          int w, int normalize, int exact, void *workspace,
                          size_t workspace_bytes, bc_stream_t stream);
 
+/* Inference forward of a whole box block tail in one pass: what BottleneckBoxConv does around the
+ * box convolution once the network is in eval mode (examples/Cityscapes/models/ENet.py:282-304,
+ * examples/Cityscapes/models/ERFNet.py:117-137 of the reference: ReLU, BoxConv2d, BatchNorm2d,
+ * residual add, ReLU as separate PyTorch operators, each a full read and write of its tensor):
+ *   out[n, k] = act( out_scale[k] * box(act_in(input))[n, k] + out_shift[k] + residual[n, k] ),
+ *   k = c*F + f.
+ *   input_relu   nonzero: ReLU on the input as it is read;
+ *   out_scale, out_shift  (C*F) each, the folded BatchNorm of the output channels; NULL = 1 / 0;
+ *   residual     (N, C*F, h, w) or NULL; may be the output buffer itself (in-place skip connection);
+ *   output_relu  nonzero: ReLU on the result.
+ * No gradients.  Workspace as bc_boxconv2d_forward_workspace(). */
+int bc_boxconv2d_forward_fused(const float *input, const float *x_min, const float *x_max,
+                               const float *y_min, const float *y_max, float reparametrization_h,
+                               float reparametrization_w, float *output, int N, int C, int F, int h,
+                               int w, int normalize, int exact, int input_relu, const float *out_scale,
+                               const float *out_shift, const float *residual, int output_relu,
+                               void *workspace, size_t workspace_bytes, bc_stream_t stream);
+
 size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask);
 int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x_max,
                           const float *y_min, const float *y_max, const float *grad_output,
