@@ -3,6 +3,9 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
 
+(`--workload cfg4` times the integral image alone, `--workload infer` the batch-1 inference block
+tails of one frame; the default and the contract line are cfg2.)
+
 One step = one training pass of the box block over one batch of synthetic input: parameter
 clip, forward, backward (grad-input and the four parameter gradients) and, on more than one GPU,
 the all-reduce of the packed (4, C, F) parameter gradient.  Each rank works on its own batch of
@@ -151,6 +154,163 @@ def run_reference(args, rank, world):
                    "os_cpu_count": os.cpu_count()},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# inference workload: the box-block tails of BoxENet on one 512 x 1024 frame
+# ------------------------------------------------------------------------------------------
+# (count, C = bottleneck channels, F, h, w): BottleneckBoxConv(128,4,h/8,w/8) x8, (64,4,h/4,w/4) x3 and
+# (16,2,h/2,w/2) x1 of the reference's BoxENet (examples/Cityscapes/models/ENet.py:61-105), batch 1,
+# rounded boxes (exact=False) and BatchNorm/Dropout removed as its runtime script does
+# (examples/Cityscapes/convnet-runtime-benchmark.py:38-53): per block ReLU -> BoxConv2d -> + skip -> ReLU.
+INFER_LAYERS = [(8, 32, 4, 64, 128), (3, 16, 4, 128, 256), (1, 8, 2, 256, 512)]
+INFER_METRIC = "BoxENet box-block tails per 512x1024 frame, batch 1"
+
+
+def infer_inputs(C, F, h, w, seed, device=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((1, C, h, w), generator=g)
+    skip = torch.randn((1, C * F, h, w), generator=g)
+    return (x.to(device), skip.to(device)) if device is not None else (x, skip)
+
+
+def infer_module(cls, C, F, h, w, seed):
+    import random
+    random.seed(seed)                       # reset_parameters draws from Python's generator
+    m = cls(C, F, h, w, reparametrization_factor=0.86)
+    m.exact = False
+    return m
+
+
+def run_infer(args, rank, world, local_rank):
+    """Latency of the box-block tails of one frame: every rank runs the same frame (replicas)."""
+    import box_convolution as bc
+    from box_convolution import _cabi
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    per_layer = []
+    launches0 = _cabi.lib.bc_launch_count()
+    t_start = time.perf_counter()
+    total = {"unfused_eager": 0.0, "fused_eager": 0.0, "fused_graph": 0.0, "fused_graph_cold": 0.0}
+    for li, (count, C, F, h, w) in enumerate(INFER_LAYERS):
+        m = infer_module(bc.BoxConv2d, C, F, h, w, 100 + li).to(dev).eval()
+        # enough distinct (input, skip, output) sets to exceed the 126 MB L2 for the cold figure
+        set_bytes = 4 * h * w * (C + 2 * C * F)
+        nsets = max(2, int(140e6 // set_bytes) + 1)
+        sets = [infer_inputs(C, F, h, w, 1000 * li + i, dev) for i in range(nsets)]
+
+        def unfused(x, skip):
+            with torch.no_grad():
+                return (skip + m(torch.relu(x))).relu_()
+
+        def fused(x, skip):
+            return bc.fused_box_block(m, x, input_relu=True, residual=skip, output_relu=True)
+
+        def timed(fn, rotate):
+            for i in range(W):
+                fn(*sets[i % nsets if rotate else 0])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(K):
+                fn(*sets[i % nsets if rotate else 0])
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / K          # us per call
+
+        graphs = [bc.GraphedForward(fused, *sets[i]) for i in range(nsets)]
+        it = [0]
+
+        def graph_hot(x, skip):
+            return graphs[0].replay()
+
+        def graph_cold(x, skip):
+            it[0] += 1
+            return graphs[it[0] % nsets].replay()
+
+        r = {"layer": "BoxConv2d(%d,%d,%d,%d)" % (C, F, h, w), "per_frame": count,
+             "unfused_eager_us": timed(unfused, True), "fused_eager_us": timed(fused, True),
+             "fused_graph_us": timed(graph_hot, False), "fused_graph_cold_us": timed(graph_cold, False)}
+        want = unfused(*sets[0])
+        err = (fused(*sets[0]) - want).abs().max().item() / max(1.0, want.abs().max().item())
+        r["max_rel_err_vs_unfused"] = err
+        per_layer.append(r)
+        for k in total:
+            total[k] += count * r[k + "_us"]
+        del graphs, sets
+        stage("inference layer %d done" % li)
+    t_end = time.perf_counter()
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    if rank != 0:
+        return
+    line = {
+        "metric": INFER_METRIC, "value": total["fused_graph_cold"], "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": total["fused_graph_cold"] / 1e3, "higher_is_better": False, "scaling": "replicas", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "infer: per block ReLU -> BoxConv2d(exact=False) -> + skip -> ReLU, eval mode, batch 1; "
+                               "8 x (32,4,64,128) + 3 x (16,4,128,256) + 1 x (8,2,256,512)",
+                   "l2": "value and *_eager figures rotate over buffer sets larger than L2; fused_graph_us reuses one set (L2-resident, as inside a network)"},
+        "totals_us": total, "layers": per_layer,
+        "gpu_launches": int(_cabi.lib.bc_launch_count() - launches0),
+        "clocks": sampler.summary(t_start, t_end),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_infer_reference(args, rank, world):
+    """The same block tails through the reference's CPU extension, driven as its autograd Function
+    drives it (integral_image -> box_convolution_forward), all host threads torch gives it."""
+    if rank != 0:
+        return
+    from oracle import build_ref, oracle
+    ext = build_ref.load_ref()
+    kind = "reference" if ext is not None else "port"
+    sys.path.insert(0, os.path.join(ROOT, "box-convolutions_b200"))
+    import random
+    total, per_layer = 0.0, []
+    reps = max(1, min(args.steps, 3))
+    for li, (count, C, F, h, w) in enumerate(INFER_LAYERS):
+        # same boxes as our arm: the reference's own initialisation rule, seeded alike
+        from box_convolution.module import BoxConv2d
+        m = infer_module(BoxConv2d, C, F, h, w, 100 + li)
+        pix = [p.detach() * f for p, f in zip((m.x_min, m.x_max, m.y_min, m.y_max),
+                                              (m.reparametrization_h, m.reparametrization_h,
+                                               m.reparametrization_w, m.reparametrization_w))]
+        x, skip = infer_inputs(C, F, h, w, 1000 * li)
+
+        def block():
+            xr = torch.relu(x)
+            if ext is not None:
+                out = ext.box_convolution_forward(ext.integral_image(xr), *pix, True, False)
+            else:
+                integ = oracle.integral_image(xr.numpy())
+                out = torch.from_numpy(oracle.box_convolution_forward(integ, *[p.numpy() for p in pix], True, False))
+            return (skip + out.view_as(skip)).relu_()
+
+        block()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            block()
+        us = (time.perf_counter() - t0) / reps * 1e6
+        per_layer.append({"layer": "BoxConv2d(%d,%d,%d,%d)" % (C, F, h, w), "per_frame": count, "us": us})
+        total += count * us
+    cores = torch.get_num_threads() if ext is not None else 1
+    line = {
+        "impl": "reference", "metric": INFER_METRIC, "value": total, "unit": "us", "n_gpus": args.gpus,
+        "steps": reps, "warmup": 1, "ms_per_step": total / 1e3, "higher_is_better": False, "scaling": "replicas",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "infer (see the main arm)", "host_threads": cores, "os_cpu_count": os.cpu_count()},
+        "layers": per_layer,
+        "cpu_baseline": {"value": total, "unit": "us", "cores": cores, "kind": kind,
+                         "sample": "each of the three layer shapes timed %d times, scaled by its count per frame" % reps},
+        "e2e": {"value": total, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -547,7 +707,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS) + ["cfg4"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS) + ["cfg4", "infer"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
@@ -566,12 +726,17 @@ def main():
     if args.impl == "reference":
         if args.workload == "cfg4":
             raise SystemExit("--impl reference supports the BoxConv2d workloads; cfg4 prints its CPU baseline in the main line")
-        run_reference(args, rank, world)
+        if args.workload == "infer":
+            run_infer_reference(args, rank, world)
+        else:
+            run_reference(args, rank, world)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py --impl ours needs a GPU: the CUDA library has no CPU fallback")
         if args.workload == "cfg4":
             run_integral(args, rank, world, local_rank)
+        elif args.workload == "infer":
+            run_infer(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
 
