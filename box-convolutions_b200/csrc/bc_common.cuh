@@ -50,7 +50,7 @@ int check_launch(const char *what);
 // Kernel ids reported by the profiling aid (bc_profile_get / bc_kernel_name).
 enum KernelId {
     KID_INTEGRAL = 1, KID_FORWARD_GLOBAL, KID_BACKWARD_GLOBAL, KID_FINISH_PARAM_GRADS, KID_CLIP,
-    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_BACKWARD_BAND, KID_COUNT
+    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_BACKWARD_BAND, KID_INTEGRAL_BANDS, KID_COUNT
 };
 
 // Put around a kernel launch: counts it and, while profiling is enabled, records a CUDA event on

@@ -475,6 +475,7 @@ const char *bc_kernel_name(int kernel_id)
         case KID_BACKWARD_PLANE: return "backward_plane_kernel";
         case KID_SUM_CHUNKS: return "sum_chunk_grads_kernel";
         case KID_BACKWARD_BAND: return "backward_band_kernel";
+        case KID_INTEGRAL_BANDS: return "integral_band_fixup_kernels";
         default: return "unknown";
     }
 }

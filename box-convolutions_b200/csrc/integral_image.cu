@@ -77,7 +77,8 @@ __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n
 // planes) the kernel stays small in registers and relies on many resident CTAs.
 template <bool VEC4, bool PIPELINED>
 __global__ void __launch_bounds__(kMaxThreads)
-integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int h, int w, int tile_rows, bool relu)
+integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int plane_h, int w, int tile_rows, bool relu,
+                      int band_rows, int nbands)
 {
     extern __shared__ float4 smem4[];
     float *tile = reinterpret_cast<float *>(smem4);           // tile_rows*(w+1) + 4 floats
@@ -86,16 +87,21 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kThreads = blockDim.x, kWarps = blockDim.x >> 5;
-    const int64_t plane = blockIdx.x;
-    const float *src = in + plane * (int64_t)h * w;
-    float *dst = out + plane * (int64_t)(h + 1) * pw;
+    // a CTA integrates rows [band*band_rows, +h) of its plane on their own (nbands = 1: the whole
+    // plane); with more bands two small kernels afterwards add what lies above each band
+    const int64_t plane = blockIdx.x / nbands;
+    const int band = blockIdx.x % nbands;
+    const int h = min(band_rows, plane_h - band * band_rows);
+    const float *src = in + plane * (int64_t)plane_h * w + (int64_t)band * band_rows * w;
+    float *dst = out + plane * (int64_t)(plane_h + 1) * pw + (int64_t)band * band_rows * pw;
     const int n4 = w >> 2;
     float4 pre[kBatch];      // dead in the instantiations that are not PIPELINED
     if (PIPELINED && warp < tile_rows && warp < h)
         load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre, relu);
 
     for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
-    for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
+    if (band == 0)
+        for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
 
     for (int r0 = 0; r0 < h; r0 += tile_rows) {
         const int rows = min(tile_rows, h - r0);
@@ -245,6 +251,55 @@ integral_image_f64_kernel(const double *__restrict__ in, double *__restrict__ ou
     }
 }
 
+// After the bands of a plane have been integrated separately: the last row of band b' (row
+// (b'+1)*band_rows of the output) holds that band's column totals.  This kernel adds the totals of
+// all bands above to every row of a band except its own last row, which other CTAs are reading;
+// the last rows are finished afterwards by band_last_rows_kernel.  The final band has no readers
+// and is updated whole.
+__global__ void __launch_bounds__(256)
+band_add_above_kernel(float *__restrict__ out, int plane_h, int w, int band_rows, int nbands, int col_chunks)
+{
+    const int pw = w + 1;
+    int b = blockIdx.x;
+    const int chunk = b % col_chunks; b /= col_chunks;
+    const int band = 1 + b % (nbands - 1);
+    const int64_t plane = b / (nbands - 1);
+    const int c = 1 + chunk * 256 + threadIdx.x;           // column 0 is zero everywhere
+    if (c >= pw) return;
+    float *base = out + plane * (int64_t)(plane_h + 1) * pw + c;
+    float above = 0.0f;
+    for (int k = 1; k <= band; ++k) above += base[(int64_t)k * band_rows * pw];
+    const int r0 = band * band_rows + 1;
+    const int r1 = band == nbands - 1 ? plane_h + 1 : (band + 1) * band_rows;    // exclusive
+    int r = r0;
+    for (; r + 8 <= r1; r += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = base[(int64_t)(r + k) * pw];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) base[(int64_t)(r + k) * pw] = v[k] + above;
+    }
+    for (; r < r1; ++r) base[(int64_t)r * pw] += above;
+}
+
+// Running sum down the last rows of bands 0 .. nbands-2, one thread per (plane, column).
+__global__ void band_last_rows_kernel(float *__restrict__ out, int64_t planes, int plane_h, int w, int band_rows,
+                                      int nbands)
+{
+    const int pw = w + 1;
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= planes * w) return;
+    const int64_t plane = i / w;
+    const int c = 1 + (int)(i - plane * w);
+    float *base = out + plane * (int64_t)(plane_h + 1) * pw + c;
+    float run = 0.0f;
+    for (int k = 1; k < nbands; ++k) {
+        const float v = base[(int64_t)k * band_rows * pw];
+        base[(int64_t)k * band_rows * pw] = v + run;
+        run += v;
+    }
+}
+
 }  // namespace
 
 // Shared memory a CTA needs for tiles of `tile_rows` rows.
@@ -288,15 +343,28 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const int pw = w + 1;
     const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
-    // rows per tile: about 36 KB of shared memory, never more than the plane has
+    // Few tall planes cannot fill the GPU with one CTA each (a CTA walks down its plane tile by
+    // tile): cut every plane into bands of rows that are integrated side by side, then add what
+    // lies above each band (two more small launches over data that is still in L2).
+    int band_rows = h, nbands = 1;
+    if (planes < 148 && h >= 64 && w >= 1) {
+        const int want = (int)((2 * 148 + planes - 1) / planes);          // bands per plane for ~2 CTAs per SM
+        int rows = (h + want - 1) / want;
+        rows = ((rows < 16 ? 16 : rows) + 7) & ~7;
+        if (rows < h) {
+            band_rows = rows;
+            nbands = (h + rows - 1) / rows;
+        }
+    }
+    // rows per tile: about 36 KB of shared memory, never more than a band has
     int tile_rows = 9000 / pw;
-    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && h >= 2 * (kMaxThreads / 32);
+    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && band_rows >= 2 * (kMaxThreads / 32);
     if (pipelined) tile_rows = kMaxThreads / 32;
     if (tile_rows < 1) tile_rows = 1;
-    if (tile_rows > h) tile_rows = h > 0 ? h : 1;
+    if (tile_rows > band_rows) tile_rows = band_rows > 0 ? band_rows : 1;
     const size_t smem = tile_smem_bytes(tile_rows, w);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
-    void (*kern)(const float *, float *, int, int, int, bool) =
+    void (*kern)(const float *, float *, int, int, int, bool, int, int) =
         pipelined ? integral_image_kernel<true, true>
                   : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
     if (smem > 48 * 1024) {
@@ -305,9 +373,23 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
-        kern<<<(unsigned)planes, kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in);
+        kern<<<(unsigned)(planes * nbands), kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in, band_rows, nbands);
     }
-    return check_launch("integral_image");
+    int st = check_launch("integral_image");
+    if (st != BC_OK || nbands == 1) return st;
+    const int col_chunks = (w + 255) / 256;
+    {
+        LaunchScope scope(KID_INTEGRAL_BANDS, s);
+        band_add_above_kernel<<<(unsigned)(planes * (nbands - 1) * col_chunks), 256, 0, s>>>(out, h, w, band_rows, nbands,
+                                                                                           col_chunks);
+    }
+    st = check_launch("integral_image (bands)");
+    if (st != BC_OK || nbands == 2) return st;       // two bands: the only last row with readers is band 0's, already final
+    {
+        LaunchScope scope(KID_INTEGRAL_BANDS, s);
+        band_last_rows_kernel<<<(unsigned)((planes * w + 255) / 256), 256, 0, s>>>(out, planes, h, w, band_rows, nbands);
+    }
+    return check_launch("integral_image (band rows)");
 }
 
 }  // namespace bc
