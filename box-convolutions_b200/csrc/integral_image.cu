@@ -39,25 +39,26 @@ __device__ __forceinline__ float4 relu4(float4 v)
     return make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
 }
 
-__device__ __forceinline__ void load_segments(const float4 *row4, int n4, int seg0, int lane, float4 (&buf)[kBatch], bool relu)
+__device__ __forceinline__ void load_segments(const float4 *row4, int n4, int seg0, int lane, float4 (&buf)[kBatch])
 {
 #pragma unroll
     for (int k = 0; k < kBatch; ++k) {
         const int j = (seg0 + k) * 32 + lane;
         buf[k] = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (relu) buf[k] = relu4(buf[k]);
     }
 }
 
 // Prefix-sums the loaded segments along the row (carry `running` joins segments and batches) and
 // writes them to the tile row at columns c+1.
+// (the optional ReLU is applied here, where the values are consumed, so that the loads of the
+// next tile stay in flight untouched)
 __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n4, int seg0, int lane, int w,
-                                              float *trow, float &running)
+                                              float *trow, float &running, bool relu)
 {
 #pragma unroll
     for (int k = 0; k < kBatch; ++k) {
         if ((seg0 + k) * 32 < n4) {
-            float4 v = buf[k];
+            float4 v = relu ? relu4(buf[k]) : buf[k];
             v.y += v.x; v.z += v.y; v.w += v.z;
             const float incl = warp_inclusive_scan(v.w, lane);
             const float add = running + (incl - v.w);
@@ -97,7 +98,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     const int n4 = w >> 2;
     float4 pre[kBatch];      // dead in the instantiations that are not PIPELINED
     if (PIPELINED && warp < tile_rows && warp < h)
-        load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre, relu);
+        load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre);
 
     for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
     if (band == 0)
@@ -115,11 +116,11 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
                 float *trow = t + warp * pw;
                 if (lane == 0) trow[0] = 0.0f;
                 float running = 0.0f;
-                scan_segments(pre, n4, 0, lane, w, trow, running);
+                scan_segments(pre, n4, 0, lane, w, trow, running, relu);
             }
             const int rn = r0 + tile_rows + warp;
             if (warp < tile_rows && rn < h)
-                load_segments(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, 0, lane, pre, relu);
+                load_segments(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, 0, lane, pre);
         } else {
             for (int i = warp; i < rows; i += kWarps) {
                 const float *row = src + (int64_t)(r0 + i) * w;
@@ -343,11 +344,11 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const int pw = w + 1;
     const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
-    // Few tall planes cannot fill the GPU with one CTA each (a CTA walks down its plane tile by
+    // A few tall planes (at most 64) cannot fill the GPU with one CTA each (a CTA walks down its plane tile by
     // tile): cut every plane into bands of rows that are integrated side by side, then add what
     // lies above each band (two more small launches over data that is still in L2).
     int band_rows = h, nbands = 1;
-    if (planes < 148 && h >= 64 && w >= 1) {
+    if (planes <= 64 && h >= 64 && w >= 1) {
         const int want = (int)((2 * 148 + planes - 1) / planes);          // bands per plane for ~2 CTAs per SM
         int rows = (h + want - 1) / want;
         rows = ((rows < 16 ? 16 : rows) + 7) & ~7;
