@@ -156,3 +156,59 @@ def test_mixed_dtypes_are_rejected():
     p32 = [torch.zeros(1, 1, device="cuda") for _ in range(4)]
     with pytest.raises(RuntimeError):
         ext.box_convolution_forward(xi, *p32, False, True)
+
+
+def test_reference_style_random_cases_fp32():
+    """The reference's own test loop (box_convolution/test.py:186-274 of the reference), restated:
+    40 random single-plane cases with h, w <= 10, 70 % exact / 30 % rounded boxes, random
+    normalisation and reparametrization factor, sparse 0/1 grad_output; the float32 module against the
+    dense float64 restatement with the reference's tolerances (rtol 3e-5, atol 1e-5), and the
+    parameter clip must leave the test's boxes alone."""
+    import random
+    from box_convolution import BoxConv2d
+    rnd = random.Random(1546545757)
+    rng = np.random.default_rng(1546545757)
+    for case in range(40):
+        h, w = rnd.randint(1, 10), rnd.randint(1, 10)
+        exact = rnd.random() < 0.7
+        normalize = rnd.random() < 0.5
+        factor = rnd.uniform(0.5, 5.0)
+        m = BoxConv2d(1, 1, h + 1, w + 1, reparametrization_factor=factor, normalize=normalize).cuda()
+        m.exact = exact
+        # a box inside the clip range, every coordinate at least 0.012 from a whole number
+        def coord(lo, hi):
+            while True:
+                v = rnd.uniform(lo, hi)
+                if abs(v - round(v)) >= 0.012:
+                    return v
+        x_min = coord(-h * 0.9, h * 0.5); x_max = coord(x_min + 1.1, x_min + h)
+        y_min = coord(-w * 0.9, w * 0.5); y_max = coord(y_min + 1.1, y_min + w)
+        x_max, y_max = min(x_max, h - 0.5 + 0.25), min(y_max, w - 0.5 + 0.25)
+        if x_max - x_min < 1.1 or y_max - y_min < 1.1 or min(abs(v - round(v)) for v in (x_max, y_max)) < 0.012:
+            continue
+        pixels = [x_min, x_max, y_min, y_max]
+        with torch.no_grad():
+            for p, v, r in zip((m.x_min, m.x_max, m.y_min, m.y_max), pixels,
+                               (m.reparametrization_h, m.reparametrization_h, m.reparametrization_w, m.reparametrization_w)):
+                p.fill_(v / r)
+        before = [p.detach().clone() for p in m.parameters()]
+        x = torch.tensor(rng.random((1, 1, h, w), dtype=np.float32), device="cuda", requires_grad=True)
+        go = torch.tensor((rng.random((1, 1, h, w)) < 0.3).astype(np.float32), device="cuda")
+        y = m(x)                                    # training mode: clips first
+        for a, b in zip(m.parameters(), before):
+            assert torch.equal(a.detach(), b), "clip altered the test's box (case %d)" % case
+        y.backward(go)
+
+        used = [p.detach().double() * r for p, r in zip(
+            (m.x_min, m.x_max, m.y_min, m.y_max),
+            (m.reparametrization_h, m.reparametrization_h, m.reparametrization_w, m.reparametrization_w))]
+        if not exact:
+            used = [torch.ceil(used[0]), torch.floor(used[1]), torch.ceil(used[2]), torch.floor(used[3])]
+        xd = x.detach().double().requires_grad_()
+        want = dense_boxconv(xd, *used, False)
+        if normalize:
+            # the reference divides by the area of the box as used (rounded boxes: of the rounded box)
+            want = want / ((used[1] - used[0] + 1) * (used[3] - used[2] + 1))
+        want_gin, = torch.autograd.grad(want, xd, go.double())
+        assert torch.allclose(y.detach().double(), want.detach(), rtol=3e-5, atol=1e-5), case
+        assert torch.allclose(x.grad.double(), want_gin, rtol=3e-5, atol=1e-5), case
