@@ -3,6 +3,10 @@
 sm_100a library.  Code written against ``box_convolution_cpp_cuda`` can import this module in
 its place.  Tensors must be CUDA float32 or float64 (all arguments of one call in the same type);
 there is no CPU implementation.
+
+float16 and bfloat16 tensors are accepted as well, as storage types only: they are widened to float32
+on the device, the float32 kernels run, and results are rounded back to the caller's type (the
+reference runs its arithmetic in half precision, integral images included; nothing here does).
 """
 import torch
 
@@ -24,6 +28,22 @@ def _require_cuda_float(t, name, dtype=None):
         raise RuntimeError("box_convolution: %s must be float32 or float64, got %s" % (name, t.dtype))
     if dtype is not None and t.dtype != dtype:
         raise RuntimeError("box_convolution: %s is %s but the call's other tensors are %s" % (name, t.dtype, dtype))
+
+
+_NARROW = (torch.float16, torch.bfloat16)
+
+
+def _widen(tensors):
+    """(float32 copies of the tensors, the narrow dtype they had) if the first one is float16 or
+    bfloat16, else (the tensors, None)."""
+    first = next((t for t in tensors if isinstance(t, torch.Tensor)), None)
+    if first is None or first.dtype not in _NARROW:
+        return tensors, None
+    narrow = first.dtype
+    for t in tensors:
+        if isinstance(t, torch.Tensor) and t.numel() and t.dtype != narrow:
+            raise RuntimeError("box_convolution: tensors of one call must share a dtype, got %s and %s" % (narrow, t.dtype))
+    return [t.float() if isinstance(t, torch.Tensor) and t.numel() else t for t in tensors], narrow
 
 
 def _entry(name, dtype):
@@ -53,6 +73,9 @@ def _workspace(nbytes, device):
 def integral_image(input):
     """(..., h, w) -> (..., h+1, w+1) zero-padded 2-D prefix sum.
     Mirrors src/integral_image_interface.cpp:8-27."""
+    (input,), narrow = _widen([input])
+    if narrow is not None:
+        return integral_image(input).to(narrow)
     _require_cuda_float(input, "input")
     if input.dim() < 2:
         raise RuntimeError("integral image input must have >=2 dimensions")
@@ -67,6 +90,9 @@ def integral_image(input):
 
 def box_convolution_forward(input_integrated, x_min, x_max, y_min, y_max, normalize, exact):
     """Mirrors src/box_convolution_interface.cpp:13-139.  Parameters are in actual pixels."""
+    wide, narrow = _widen([input_integrated, x_min, x_max, y_min, y_max])
+    if narrow is not None:
+        return box_convolution_forward(*wide, normalize, exact).to(narrow)
     _require_cuda_float(input_integrated, "input_integrated")
     dtype = input_integrated.dtype
     if input_integrated.device != x_min.device:
@@ -93,6 +119,12 @@ def box_convolution_backward(
     """Mirrors src/box_convolution_interface.cpp:141-395: returns
     [grad_input, grad_x_min, grad_x_max, grad_y_min, grad_y_max]; entries not asked for are
     0-element tensors (interface.cpp:182,394).  `output` is accepted and ignored."""
+    wide, narrow = _widen([input_integrated, x_min, x_max, y_min, y_max, grad_output])
+    if narrow is not None:
+        grads = box_convolution_backward(
+            *wide, None, reparametrization_h, reparametrization_w, normalize, exact,
+            input_needs_grad, x_min_needs_grad, x_max_needs_grad, y_min_needs_grad, y_max_needs_grad)
+        return [g.to(narrow) for g in grads]
     _require_cuda_float(input_integrated, "input_integrated")
     dtype = input_integrated.dtype
     _require_cuda_float(grad_output, "grad_output", dtype)
@@ -131,6 +163,13 @@ def box_convolution_backward(
 def clip_parameters(x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
                     max_input_h, max_input_w, exact):
     """In place.  Mirrors src/box_convolution_interface.cpp:397-415."""
+    wide, narrow = _widen([x_min, x_max, y_min, y_max])
+    if narrow is not None:
+        clip_parameters(*wide, reparametrization_h, reparametrization_w, max_input_h, max_input_w, exact)
+        with torch.no_grad():
+            for p, v in zip((x_min, x_max, y_min, y_max), wide):
+                p.copy_(v)
+        return
     ps = (x_min, x_max, y_min, y_max)
     for p, n in zip(ps, ("x_min", "x_max", "y_min", "y_max")):
         _require_cuda_float(p, n, x_min.dtype if isinstance(x_min, torch.Tensor) else None)

@@ -8,7 +8,9 @@ takes from the saved output is recomputed, so only the input and the four parame
 kept alive between forward and backward.
 
 float64 tensors (gradient checks) take the general kernels through the four extension functions,
-chained as the reference chains them.
+chained as the reference chains them.  float16 / bfloat16 tensors are storage only: the Function
+widens them to float32 on the device, runs the float32 kernels and rounds results and gradients
+back.
 """
 import torch
 
@@ -41,6 +43,16 @@ class BoxConvolutionFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, x_min, x_max, y_min, y_max,
                 reparametrization_h, reparametrization_w, normalize, exact):
+        ctx.narrow = None
+        if isinstance(input, torch.Tensor) and input.dtype in ext._NARROW:
+            (input, x_min, x_max, y_min, y_max), ctx.narrow = ext._widen([input, x_min, x_max, y_min, y_max])
+        out = BoxConvolutionFunction._forward_wide(ctx, input, x_min, x_max, y_min, y_max, reparametrization_h,
+                                                   reparametrization_w, normalize, exact)
+        return out if ctx.narrow is None else out.to(ctx.narrow)
+
+    @staticmethod
+    def _forward_wide(ctx, input, x_min, x_max, y_min, y_max,
+                      reparametrization_h, reparametrization_w, normalize, exact):
         _require_cuda_float(input, "input")
         if input.dim() != 4:
             raise RuntimeError("BoxConv2d: input must have 4 dimensions")
@@ -83,6 +95,13 @@ class BoxConvolutionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if ctx.narrow is not None:
+            grads = BoxConvolutionFunction._backward_wide(ctx, grad_output.float())
+            return tuple(g.to(ctx.narrow) if g is not None else None for g in grads)
+        return BoxConvolutionFunction._backward_wide(ctx, grad_output)
+
+    @staticmethod
+    def _backward_wide(ctx, grad_output):
         if ctx.chained:
             input_integrated, x_min, x_max, y_min, y_max = ctx.saved_tensors
             needs = ctx.needs_input_grad[:5]

@@ -108,3 +108,31 @@ def test_fused_block_rejects_bad_arguments():
         fused_box_block(m, x, residual=torch.zeros(1, 4, 16, 15, device="cuda"))
     with pytest.raises(RuntimeError):
         fused_box_block(m, x.cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_narrow_storage_types_run_in_float32(dtype):
+    """half / bfloat16 modules and tensors: same results as the float32 run of the same (rounded)
+    values, up to the rounding of the stored result."""
+    from box_convolution import BoxConv2d, integral_image
+    import random
+    random.seed(5)
+    m32 = BoxConv2d(3, 2, 32, 48).cuda()
+    m16 = BoxConv2d(3, 2, 32, 48).cuda().to(dtype)
+    with torch.no_grad():
+        for a, b in zip(m16.parameters(), m32.parameters()):
+            a.copy_(b)
+            b.copy_(a.float())                 # both modules hold the same (rounded) boxes
+    x16 = torch.randn(2, 3, 32, 48, device="cuda").to(dtype).requires_grad_()
+    x32 = x16.detach().float().requires_grad_()
+    y16, y32 = m16(x16), m32(x32)
+    assert y16.dtype == dtype
+    assert torch.equal(y16, y32.to(dtype))
+    g = torch.randn_like(y32).to(dtype)
+    y16.backward(g)
+    y32.backward(g.float())
+    assert x16.grad.dtype == dtype and torch.equal(x16.grad, x32.grad.to(dtype))
+    for a, b in zip(m16.parameters(), m32.parameters()):
+        assert a.grad.dtype == dtype and torch.equal(a.grad, b.grad.to(dtype))
+    ii = integral_image(x16.detach())
+    assert ii.dtype == dtype and torch.equal(ii, integral_image(x32.detach()).to(dtype))
