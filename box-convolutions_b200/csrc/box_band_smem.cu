@@ -146,8 +146,11 @@ backward_band_kernel(const float *__restrict__ x, const float *__restrict__ go_i
         __syncthreads();
 
         const ColW2 cw = col_weights(t);
-        float s_out = 0.f, left1 = 0.f, right1 = 0.f;
-        f2_t topbot2 = pack2(0.f, 0.f), left2 = pack2(0.f, 0.f), right2 = pack2(0.f, 0.f);
+        // sums over the strip of x times the column-strip values of the four tap rows, kept per
+        // tap-row pair: *P = (row lo-1, row hi), *Q = (row lo, row hi+1); combined after the walk
+        float s_out = 0.f;
+        f2_t topbot2 = pack2(0.f, 0.f);
+        f2_t leftP = pack2(0.f, 0.f), leftQ = pack2(0.f, 0.f), rightP = pack2(0.f, 0.f), rightQ = pack2(0.f, 0.f);
         if (active) {
             if (NEED_PARAMS) {
                 f2_t pd[kStrip], pel[kStrip], peh[kStrip];
@@ -178,14 +181,11 @@ backward_band_kernel(const float *__restrict__ x, const float *__restrict__ go_i
                             topbot2 = fma2(xx, dd, topbot2);
                             s_out += xv[m] * gg;
                             gin[i][m] += gg * t.scale;
-                            unpack2(cel[m], lo_new, hi_new);
-                            unpack2(pel[m], lo_old, hi_old);
-                            left2 = fma2(xx, sub2(cel[m], pel[m]), left2);
-                            left1 += xv[m] * (hi_old - lo_new);
-                            unpack2(ceh[m], lo_new, hi_new);
-                            unpack2(peh[m], lo_old, hi_old);
-                            right2 = fma2(xx, sub2(ceh[m], peh[m]), right2);
-                            right1 += xv[m] * (hi_old - lo_new);
+                            // e_lo / e_hi: the two column strips
+                            leftP = fma2(xx, pel[m], leftP);
+                            leftQ = fma2(xx, cel[m], leftQ);
+                            rightP = fma2(xx, peh[m], rightP);
+                            rightQ = fma2(xx, ceh[m], rightQ);
                             pd[m] = cd[m]; pel[m] = cel[m]; peh[m] = ceh[m];
                         }
                     }
@@ -214,13 +214,15 @@ backward_band_kernel(const float *__restrict__ x, const float *__restrict__ go_i
             }
         }
         if (NEED_PARAMS) {
-            float tb_top, tb_bot, l_lo, l_hi, r_lo, r_hi;
+            float tb_top, tb_bot, la, lc, lb, ld, ra, rc, rb, rd;
             unpack2(topbot2, tb_top, tb_bot);
-            unpack2(left2, l_lo, l_hi);
-            unpack2(right2, r_lo, r_hi);
+            unpack2(leftP, la, lc);
+            unpack2(leftQ, lb, ld);
+            unpack2(rightP, ra, rc);
+            unpack2(rightQ, rb, rd);
             float v[kNumSums] = {s_out, tb_top, tb_bot,
-                                 left1 + t.f_lo_r * l_lo + t.f_hi_r * l_hi,
-                                 right1 + t.f_lo_r * r_lo + t.f_hi_r * r_hi};
+                                 combine_rows(la, lb, lc, ld, t.f_lo_r, t.f_hi_r),
+                                 combine_rows(ra, rb, rc, rd, t.f_lo_r, t.f_hi_r)};
 #pragma unroll
             for (int j = 0; j < kNumSums; ++j) v[j] = warp_sum(v[j]);
             if (lane == 0) {
