@@ -289,7 +289,7 @@ __device__ __forceinline__ Walk make_walk(uint32_t sI32, const BoxTaps &t, int q
 // FUSED: the inference steps of `Fusion` around the gather (the output may then alias the residual,
 // so it is not declared restrict).
 template <int T, bool FAST, bool FUSED = false>
-__global__ void __launch_bounds__(256, T == 1 ? 4 : 1)
+__global__ void __launch_bounds__(T == 1 ? 256 : 512, T == 1 ? 4 : 1)
 forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *out, int C, int F,
                      int h, int w, int fsplit, bool normalize, bool exact, Fusion fu)
 {
@@ -664,17 +664,18 @@ static int launch_forward_plane_impl(const float *x, const BoxParams &bp, const 
     if (planes * fsplit > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
     const size_t smem = forward_smem_bytes(h, w);
     const int tiles = warp_tiles(h, w);
-    const int T = tiles > 16 ? 4 : (tiles > 8 ? 2 : 1);
+    // one tile per warp up to 8 tiles, two beyond (up to 16 warps: a CTA of a large plane has the SM to itself)
+    const int T = tiles > 8 ? 2 : 1;
     const int warps = (tiles + T - 1) / T;
     const bool fast = (h % kR == 0) && (w % kStrip == 0) && aligned16(x) && aligned16(out) &&
                       (!fu || !fu->residual || aligned16(fu->residual));
     void (*kern)(const float *, BoxParams, float *, int, int, int, int, int, bool, bool, Fusion);
     if (fu) {
-        if (fast) kern = T == 1 ? forward_plane_kernel<1, true, true> : (T == 2 ? forward_plane_kernel<2, true, true> : forward_plane_kernel<4, true, true>);
-        else kern = T == 1 ? forward_plane_kernel<1, false, true> : (T == 2 ? forward_plane_kernel<2, false, true> : forward_plane_kernel<4, false, true>);
+        if (fast) kern = T == 1 ? forward_plane_kernel<1, true, true> : forward_plane_kernel<2, true, true>;
+        else kern = T == 1 ? forward_plane_kernel<1, false, true> : forward_plane_kernel<2, false, true>;
     } else {
-        if (fast) kern = T == 1 ? forward_plane_kernel<1, true> : (T == 2 ? forward_plane_kernel<2, true> : forward_plane_kernel<4, true>);
-        else kern = T == 1 ? forward_plane_kernel<1, false> : (T == 2 ? forward_plane_kernel<2, false> : forward_plane_kernel<4, false>);
+        if (fast) kern = T == 1 ? forward_plane_kernel<1, true> : forward_plane_kernel<2, true>;
+        else kern = T == 1 ? forward_plane_kernel<1, false> : forward_plane_kernel<2, false>;
     }
     int st = opt_in_smem(kern, smem);
     if (st != BC_OK) return st;
