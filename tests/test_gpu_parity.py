@@ -211,6 +211,40 @@ def test_module_random_shapes_vs_oracle(bc, shape, normalize, exact):
         assert (out.detach().view(N, C, F, h, w)[:, 0, 0] == 0).all()
 
 
+def test_module_empty_batch_and_strided_inputs(bc):
+    """A batch of zero samples gives an empty output and zero parameter gradients; inputs and
+    grad_outputs that are views with strides (channel slices, transposes) give the same results as
+    their contiguous copies."""
+    torch.manual_seed(3)
+    m = bc.BoxConv2d(3, 2, 16, 24).cuda()
+    x0 = torch.empty(0, 3, 16, 24, device="cuda", requires_grad=True)
+    y0 = m(x0)
+    assert y0.shape == (0, 6, 16, 24)
+    y0.backward(torch.empty_like(y0))
+    for p in m.parameters():
+        assert p.grad is not None and (p.grad == 0).all()
+        p.grad = None
+
+    big = torch.randn(2, 5, 16, 48, device="cuda")
+    view = big[:, 1:4, :, ::2]                       # strided in channels and columns
+    assert not view.is_contiguous()
+    xa = view.detach().requires_grad_()
+    xb = view.detach().contiguous().requires_grad_()
+    go_big = torch.randn(2, 16, 24, 6, device="cuda")
+    go = go_big.permute(0, 3, 1, 2)                  # (2, 6, 16, 24), not contiguous
+    m.eval()
+    ya, yb = m(xa), m(xb)
+    assert torch.equal(ya, yb)
+    ya.backward(go)
+    ga = [p.grad.clone() for p in m.parameters()]
+    for p in m.parameters():
+        p.grad = None
+    yb.backward(go.contiguous())
+    assert torch.equal(xa.grad, xb.grad)
+    for a, p in zip(ga, m.parameters()):
+        assert torch.equal(a, p.grad)
+
+
 def test_many_filters_take_the_general_path(bc):
     """More filters than the per-CTA tap table holds: the module falls back to the kernels that
     read integral images from global memory; results must not change."""
