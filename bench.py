@@ -378,9 +378,12 @@ class ClockSampler(threading.Thread):
 def kernel_algorithmic_bytes(kernel, N, C, F, h, w):
     E, Ei = N * C * h * w, N * C * (h + 1) * (w + 1)
     return {
-        "integral_image_kernel": None,     # depends on the plane count of the call; not the dominant kernel
+        # two launches per step on the large-plane path (input planes, then F times as many grad_output
+        # planes): mean bytes per launch
+        "integral_image_kernel": 4 * (1 + F) * (E + Ei) // 2,
         "forward_global_kernel": 4 * (Ei + F * E),
         "backward_global_kernel": 4 * (F * Ei + 2 * E),
+        "forward_band_kernel": 4 * (Ei + F * E),
         "backward_band_kernel": 4 * (F * Ei + 2 * E),
         "forward_plane_kernel": 4 * E * (1 + F),
         "backward_plane_kernel": 4 * E * (F + 2),

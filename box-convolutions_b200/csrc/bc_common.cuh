@@ -50,7 +50,7 @@ int check_launch(const char *what);
 // Kernel ids reported by the profiling aid (bc_profile_get / bc_kernel_name).
 enum KernelId {
     KID_INTEGRAL = 1, KID_FORWARD_GLOBAL, KID_BACKWARD_GLOBAL, KID_FINISH_PARAM_GRADS, KID_CLIP,
-    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_BACKWARD_BAND, KID_INTEGRAL_BANDS, KID_COUNT
+    KID_FORWARD_PLANE, KID_BACKWARD_PLANE, KID_SUM_CHUNKS, KID_BACKWARD_BAND, KID_INTEGRAL_BANDS, KID_FORWARD_BAND, KID_COUNT
 };
 
 // Put around a kernel launch: counts it and, while profiling is enabled, records a CUDA event on
@@ -92,8 +92,9 @@ int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int co
                               T *grad_params, cudaStream_t s);
 
 // float integral image with an optional ReLU on the values read
+// lpad/rpad > 0 write rows as [lpad zeros | I[a][0..w] | rpad copies of I[a][w]] (pitch lpad + w + 1 + rpad)
 int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h, int w, bool relu_in,
-                              cudaStream_t s);
+                              cudaStream_t s, int lpad = 0, int rpad = 0);
 // forward with the Fusion steps; a null `fu` is the plain forward
 int launch_forward_global_fused(const float *integ, const BoxParams &bp, const Fusion &fu, float *out, int N,
                                 int C, int F, int h, int w, bool normalize, bool exact, cudaStream_t s);
@@ -113,13 +114,20 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
 
 int read_wait_timeouts(int *count);
 
-// Column-band backward for planes that do not fit in shared memory whole (box_band_smem.cu):
-// gathers from integral images in global memory, staged band by band.
+// Column-band kernels for planes that do not fit in shared memory whole (box_band_smem.cu): they
+// gather from integral images in global memory in the padded row layout
+// (launch_integral_image_f32 with band_lpad() / band_rpad(w)), staged band by band.
+int band_lpad();
+int band_rpad(int w);
+size_t band_integral_floats(int64_t planes, int h, int w);
+bool band_path_fits_forward(int h, int w);
 bool band_path_fits_backward(int F, int h, int w);
 size_t band_partials_bytes(int N, int C, int F, int w);
-int launch_backward_band(const float *x, const float *go_integ, const BoxParams &bp, float rep_h, float rep_w,
+// null `fu` = plain forward
+int launch_forward_band(const float *integ_padded, const BoxParams &bp, const Fusion *fu, float *out, int N, int C,
+                        int F, int h, int w, bool normalize, bool exact, cudaStream_t s);
+int launch_backward_band(const float *x, const float *go_integ_padded, const BoxParams &bp, float rep_h, float rep_w,
                          int N, int C, int F, int h, int w, bool normalize, bool exact, int need_mask,
                          float *grad_input, float *grad_params, float *partials, cudaStream_t s);
-
 
 }  // namespace bc

@@ -263,7 +263,26 @@ size_t bc_boxconv2d_forward_workspace(int N, int C, int F, int h, int w)
 {
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w)) return 0;
     if (plane_path_fits_forward(F, h, w)) return 0;
+    if (band_path_fits_forward(h, w)) return align_up(band_integral_floats((int64_t)N * C, h, w) * sizeof(float), 256);
     return integral_bytes((int64_t)N * C, h, w);
+}
+
+// Forward of planes that do not fit in shared memory: integral images to the workspace (padded rows
+// for the column-band kernel where a band fits, plain rows for the general kernel otherwise).
+static int forward_from_workspace(const float *input, const BoxParams &bp, const Fusion *fu, float *output, int N,
+                                  int C, int F, int h, int w, bool normalize, bool exact, float *integ,
+                                  cudaStream_t stream)
+{
+    const bool relu_in = fu && fu->input_relu;
+    if (band_path_fits_forward(h, w)) {
+        int st = launch_integral_image_f32(input, integ, (int64_t)N * C, h, w, relu_in, stream, band_lpad(), band_rpad(w));
+        if (st != BC_OK) return st;
+        return launch_forward_band(integ, bp, fu, output, N, C, F, h, w, normalize, exact, stream);
+    }
+    int st = launch_integral_image_f32(input, integ, (int64_t)N * C, h, w, relu_in, stream);
+    if (st != BC_OK) return st;
+    if (fu) return launch_forward_global_fused(integ, bp, *fu, output, N, C, F, h, w, normalize, exact, stream);
+    return launch_forward_global<float>(integ, bp, output, N, C, F, h, w, normalize, exact, stream);
 }
 
 int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_max,
@@ -281,10 +300,8 @@ int bc_boxconv2d_forward(const float *input, const float *x_min, const float *x_
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
         workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
         return BC_ERR_WORKSPACE;
-    float *integ = static_cast<float *>(workspace);
-    int st = launch_integral_image<float>(input, integ, (int64_t)N * C, h, w, stream);
-    if (st != BC_OK) return st;
-    return launch_forward_global<float>(integ, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+    return forward_from_workspace(input, bp, nullptr, output, N, C, F, h, w, normalize != 0, exact != 0,
+                                  static_cast<float *>(workspace), stream);
 }
 
 int bc_boxconv2d_forward_fused(const float *input, const float *x_min, const float *x_max,
@@ -305,9 +322,7 @@ int bc_boxconv2d_forward_fused(const float *input, const float *x_min, const flo
         workspace_bytes < bc_boxconv2d_forward_workspace(N, C, F, h, w))
         return BC_ERR_WORKSPACE;
     float *integ = static_cast<float *>(workspace);
-    int st = launch_integral_image_f32(input, integ, (int64_t)N * C, h, w, input_relu != 0, stream);
-    if (st != BC_OK) return st;
-    return launch_forward_global_fused(integ, bp, fu, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+    return forward_from_workspace(input, bp, &fu, output, N, C, F, h, w, normalize != 0, exact != 0, integ, stream);
 }
 
 size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int need_mask)
@@ -315,10 +330,10 @@ size_t bc_boxconv2d_backward_workspace(int N, int C, int F, int h, int w, int ne
     if (!sizes_ok(N, C, F, h, w) || any_empty(N, C, F, h, w) || !(need_mask & BC_NEED_ALL)) return 0;
     if (plane_path_fits_backward(F, h, w))
         return align_up((size_t)C * F * N * kNumSums * sizeof(float), 256);
-    size_t partials = backward_partials_bytes(N, C, F, h, w);
-    if (band_path_fits_backward(F, h, w) && band_partials_bytes(N, C, F, w) > partials)
-        partials = band_partials_bytes(N, C, F, w);
-    return integral_bytes((int64_t)N * C * F, h, w) + align_up(partials, 256);
+    if (band_path_fits_backward(F, h, w))
+        return align_up(band_integral_floats((int64_t)N * C * F, h, w) * sizeof(float), 256) +
+               align_up(band_partials_bytes(N, C, F, w), 256);
+    return integral_bytes((int64_t)N * C * F, h, w) + align_up(backward_partials_bytes(N, C, F, h, w), 256);
 }
 
 int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x_max,
@@ -346,7 +361,9 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
     if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
     if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
     const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
-    const size_t ib = integral_bytes((int64_t)N * C * F, h, w);
+    const bool band = band_path_fits_backward(F, h, w);
+    const size_t ib = band ? align_up(band_integral_floats((int64_t)N * C * F, h, w) * sizeof(float), 256)
+                           : integral_bytes((int64_t)N * C * F, h, w);
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
         workspace_bytes < bc_boxconv2d_backward_workspace(N, C, F, h, w, need_mask))
         return BC_ERR_WORKSPACE;
@@ -356,11 +373,15 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                                      grad_params, static_cast<float *>(workspace), stream);
     float *go_integ = static_cast<float *>(workspace);
     float *partials = reinterpret_cast<float *>(static_cast<char *>(workspace) + ib);
-    int st = launch_integral_image<float>(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
-    if (st != BC_OK) return st;
-    if (band_path_fits_backward(F, h, w))
+    if (band) {
+        int st = launch_integral_image_f32(grad_output, go_integ, (int64_t)N * C * F, h, w, false, stream, band_lpad(),
+                                           band_rpad(w));
+        if (st != BC_OK) return st;
         return launch_backward_band(input, go_integ, bp, reparametrization_h, reparametrization_w, N, C, F, h, w,
                                     normalize != 0, exact != 0, need_mask, grad_input, grad_params, partials, stream);
+    }
+    int st = launch_integral_image<float>(grad_output, go_integ, (int64_t)N * C * F, h, w, stream);
+    if (st != BC_OK) return st;
     return launch_backward_global<float>(input, nullptr, go_integ, bp, reparametrization_h,
                                   reparametrization_w, N, C, F, h, w, normalize != 0, exact != 0,
                                   need_mask, grad_input, grad_params, partials, stream);
@@ -476,6 +497,7 @@ const char *bc_kernel_name(int kernel_id)
         case KID_SUM_CHUNKS: return "sum_chunk_grads_kernel";
         case KID_BACKWARD_BAND: return "backward_band_kernel";
         case KID_INTEGRAL_BANDS: return "integral_band_fixup_kernels";
+        case KID_FORWARD_BAND: return "forward_band_kernel";
         default: return "unknown";
     }
 }

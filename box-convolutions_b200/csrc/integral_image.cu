@@ -79,12 +79,15 @@ __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n
 template <bool VEC4, bool PIPELINED>
 __global__ void __launch_bounds__(kMaxThreads)
 integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int plane_h, int w, int tile_rows, bool relu,
-                      int band_rows, int nbands)
+                      int band_rows, int nbands, int lpad, int rpad)
 {
+    // With padding every output row is written as [lpad zeros | 0, prefix sums | rpad copies of the
+    // row's last value], the layout the column-band kernels copy their bands from (the copies
+    // take part in the column pass like ordinary columns, so they end up as copies of I[a][w]).
     extern __shared__ float4 smem4[];
-    float *tile = reinterpret_cast<float *>(smem4);           // tile_rows*(w+1) + 4 floats
-    const int pw = w + 1;
-    float *carry = tile + ((tile_rows * pw + 4 + 3) & ~3);    // w floats
+    float *tile = reinterpret_cast<float *>(smem4);           // tile_rows*pw + 4 floats
+    const int pw = lpad + w + 1 + rpad;
+    float *carry = tile + ((tile_rows * pw + 4 + 3) & ~3);    // w + rpad floats
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kThreads = blockDim.x, kWarps = blockDim.x >> 5;
@@ -100,7 +103,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     if (PIPELINED && warp < tile_rows && warp < h)
         load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre);
 
-    for (int c = tid; c < w; c += kThreads) carry[c] = 0.0f;
+    for (int c = tid; c < w + rpad; c += kThreads) carry[c] = 0.0f;
     if (band == 0)
         for (int c = tid; c < pw; c += kThreads) dst[c] = 0.0f;   // the zero row on top
 
@@ -113,10 +116,12 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
         // ---- 1. row pass
         if (PIPELINED) {
             if (warp < rows) {
-                float *trow = t + warp * pw;
+                float *trow = t + warp * pw + lpad;
                 if (lane == 0) trow[0] = 0.0f;
                 float running = 0.0f;
                 scan_segments(pre, n4, 0, lane, w, trow, running, relu);
+                if (lane < lpad) trow[-1 - lane] = 0.0f;
+                for (int j = lane; j < rpad; j += 32) trow[w + 1 + j] = running;
             }
             const int rn = r0 + tile_rows + warp;
             if (warp < tile_rows && rn < h)
@@ -124,7 +129,7 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
         } else {
             for (int i = warp; i < rows; i += kWarps) {
                 const float *row = src + (int64_t)(r0 + i) * w;
-                float *trow = t + i * pw;
+                float *trow = t + i * pw + lpad;
                 if (lane == 0) trow[0] = 0.0f;
                 float running = 0.0f;
                 if (VEC4) {
@@ -154,14 +159,16 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
                         running += __shfl_sync(0xffffffffu, incl, 31);
                     }
                 }
+                if (lane < lpad) trow[-1 - lane] = 0.0f;
+                for (int j = lane; j < rpad; j += 32) trow[w + 1 + j] = running;
             }
         }
         __syncthreads();
 
         // ---- 2. column pass (8 rows at a time in registers so that the loads overlap)
-        for (int c = tid; c < w; c += kThreads) {
+        for (int c = tid; c < w + rpad; c += kThreads) {
             float run = carry[c];
-            float *col = t + c + 1;
+            float *col = t + lpad + c + 1;
             int i = 0;
             for (; i + 8 <= rows; i += 8) {
                 float v[8];
@@ -258,15 +265,16 @@ integral_image_f64_kernel(const double *__restrict__ in, double *__restrict__ ou
 // the last rows are finished afterwards by band_last_rows_kernel.  The final band has no readers
 // and is updated whole.
 __global__ void __launch_bounds__(256)
-band_add_above_kernel(float *__restrict__ out, int plane_h, int w, int band_rows, int nbands, int col_chunks)
+band_add_above_kernel(float *__restrict__ out, int plane_h, int pw, int c0, int ncols, int band_rows, int nbands,
+                      int col_chunks)
 {
-    const int pw = w + 1;
+    // columns c0 .. c0+ncols-1 of rows of pitch pw (everything to the left of c0 is zero)
     int b = blockIdx.x;
     const int chunk = b % col_chunks; b /= col_chunks;
     const int band = 1 + b % (nbands - 1);
     const int64_t plane = b / (nbands - 1);
-    const int c = 1 + chunk * 256 + threadIdx.x;           // column 0 is zero everywhere
-    if (c >= pw) return;
+    const int c = c0 + chunk * 256 + threadIdx.x;
+    if (c >= c0 + ncols) return;
     float *base = out + plane * (int64_t)(plane_h + 1) * pw + c;
     float above = 0.0f;
     for (int k = 1; k <= band; ++k) above += base[(int64_t)k * band_rows * pw];
@@ -284,14 +292,13 @@ band_add_above_kernel(float *__restrict__ out, int plane_h, int w, int band_rows
 }
 
 // Running sum down the last rows of bands 0 .. nbands-2, one thread per (plane, column).
-__global__ void band_last_rows_kernel(float *__restrict__ out, int64_t planes, int plane_h, int w, int band_rows,
-                                      int nbands)
+__global__ void band_last_rows_kernel(float *__restrict__ out, int64_t planes, int plane_h, int pw, int c0, int ncols,
+                                      int band_rows, int nbands)
 {
-    const int pw = w + 1;
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (i >= planes * w) return;
-    const int64_t plane = i / w;
-    const int c = 1 + (int)(i - plane * w);
+    if (i >= planes * ncols) return;
+    const int64_t plane = i / ncols;
+    const int c = c0 + (int)(i - plane * ncols);
     float *base = out + plane * (int64_t)(plane_h + 1) * pw + c;
     float run = 0.0f;
     for (int k = 1; k < nbands; ++k) {
@@ -304,9 +311,9 @@ __global__ void band_last_rows_kernel(float *__restrict__ out, int64_t planes, i
 }  // namespace
 
 // Shared memory a CTA needs for tiles of `tile_rows` rows.
-static size_t tile_smem_bytes(int tile_rows, int w)
+static size_t tile_smem_bytes(int tile_rows, int w, int lpad, int rpad)
 {
-    return ((size_t)((tile_rows * (w + 1) + 4 + 3) & ~3) + (size_t)w) * sizeof(float);
+    return ((size_t)((tile_rows * (lpad + w + 1 + rpad) + 4 + 3) & ~3) + (size_t)(w + rpad)) * sizeof(float);
 }
 
 template <>
@@ -335,14 +342,15 @@ int launch_integral_image<double>(const double *in, double *out, int64_t planes,
 template <>
 int launch_integral_image<float>(const float *in, float *out, int64_t planes, int h, int w, cudaStream_t s)
 {
-    return launch_integral_image_f32(in, out, planes, h, w, false, s);
+    return launch_integral_image_f32(in, out, planes, h, w, false, s, 0, 0);
 }
 
-int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h, int w, bool relu_in, cudaStream_t s)
+int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h, int w, bool relu_in, cudaStream_t s,
+                              int lpad, int rpad)
 {
     if (planes == 0) return BC_OK;
     if (planes > 0x7fffffffLL) return BC_ERR_BAD_SHAPE;
-    const int pw = w + 1;
+    const int pw = lpad + w + 1 + rpad;
     const bool vec4 = (w % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
     // A few tall planes (at most 64) cannot fill the GPU with one CTA each (a CTA walks down its plane tile by
     // tile): cut every plane into bands of rows that are integrated side by side, then add what
@@ -363,9 +371,9 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     if (pipelined) tile_rows = kMaxThreads / 32;
     if (tile_rows < 1) tile_rows = 1;
     if (tile_rows > band_rows) tile_rows = band_rows > 0 ? band_rows : 1;
-    const size_t smem = tile_smem_bytes(tile_rows, w);
+    const size_t smem = tile_smem_bytes(tile_rows, w, lpad, rpad);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
-    void (*kern)(const float *, float *, int, int, int, bool, int, int) =
+    void (*kern)(const float *, float *, int, int, int, bool, int, int, int, int) =
         pipelined ? integral_image_kernel<true, true>
                   : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
     if (smem > 48 * 1024) {
@@ -374,21 +382,22 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
-        kern<<<(unsigned)(planes * nbands), kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in, band_rows, nbands);
+        kern<<<(unsigned)(planes * nbands), kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in, band_rows, nbands, lpad, rpad);
     }
     int st = check_launch("integral_image");
     if (st != BC_OK || nbands == 1) return st;
-    const int col_chunks = (w + 255) / 256;
+    const int c0 = lpad + 1, ncols = w + rpad;
+    const int col_chunks = (ncols + 255) / 256;
     {
         LaunchScope scope(KID_INTEGRAL_BANDS, s);
-        band_add_above_kernel<<<(unsigned)(planes * (nbands - 1) * col_chunks), 256, 0, s>>>(out, h, w, band_rows, nbands,
-                                                                                           col_chunks);
+        band_add_above_kernel<<<(unsigned)(planes * (nbands - 1) * col_chunks), 256, 0, s>>>(out, h, pw, c0, ncols, band_rows,
+                                                                                           nbands, col_chunks);
     }
     st = check_launch("integral_image (bands)");
     if (st != BC_OK || nbands == 2) return st;       // two bands: the only last row with readers is band 0's, already final
     {
         LaunchScope scope(KID_INTEGRAL_BANDS, s);
-        band_last_rows_kernel<<<(unsigned)((planes * w + 255) / 256), 256, 0, s>>>(out, planes, h, w, band_rows, nbands);
+        band_last_rows_kernel<<<(unsigned)((planes * ncols + 255) / 256), 256, 0, s>>>(out, planes, h, pw, c0, ncols, band_rows, nbands);
     }
     return check_launch("integral_image (band rows)");
 }
