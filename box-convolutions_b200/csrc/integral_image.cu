@@ -76,8 +76,9 @@ __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n
 // in flight and the next tile's row is fetched while the current tile is scanned down its columns
 // and stored, so a CTA always has a full tile of loads outstanding.  Otherwise (short rows, many
 // planes) the kernel stays small in registers and relies on many resident CTAs.
-template <bool VEC4, bool PIPELINED>
-__global__ void __launch_bounds__(kMaxThreads)
+// BIG: 512 threads per CTA, for launches of at most one CTA per SM (twice the loads in flight)
+template <bool VEC4, bool PIPELINED, bool BIG = false>
+__global__ void __launch_bounds__(BIG ? 2 * kMaxThreads : kMaxThreads)
 integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int plane_h, int w, int tile_rows, bool relu,
                       int band_rows, int nbands, int lpad, int rpad)
 {
@@ -367,22 +368,28 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     }
     // rows per tile: about 36 KB of shared memory, never more than a band has
     int tile_rows = 9000 / pw;
-    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && band_rows >= 2 * (kMaxThreads / 32);
-    if (pipelined) tile_rows = kMaxThreads / 32;
+    // with at most one CTA per SM a CTA of twice the size keeps twice the loads in flight
+    const int threads = planes * nbands <= 148 ? 2 * kMaxThreads : kMaxThreads;
+    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && band_rows >= 2 * (threads / 32);
+    if (pipelined) tile_rows = threads / 32;
     if (tile_rows < 1) tile_rows = 1;
     if (tile_rows > band_rows) tile_rows = band_rows > 0 ? band_rows : 1;
     const size_t smem = tile_smem_bytes(tile_rows, w, lpad, rpad);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
-    void (*kern)(const float *, float *, int, int, int, bool, int, int, int, int) =
-        pipelined ? integral_image_kernel<true, true>
-                  : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
+    void (*kern)(const float *, float *, int, int, int, bool, int, int, int, int);
+    if (threads > kMaxThreads)
+        kern = pipelined ? integral_image_kernel<true, true, true>
+                         : (vec4 ? integral_image_kernel<true, false, true> : integral_image_kernel<false, false, true>);
+    else
+        kern = pipelined ? integral_image_kernel<true, true>
+                         : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("integral_image: shared memory opt-in");
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
-        kern<<<(unsigned)(planes * nbands), kMaxThreads, smem, s>>>(in, out, h, w, tile_rows, relu_in, band_rows, nbands, lpad, rpad);
+        kern<<<(unsigned)(planes * nbands), threads, smem, s>>>(in, out, h, w, tile_rows, relu_in, band_rows, nbands, lpad, rpad);
     }
     int st = check_launch("integral_image");
     if (st != BC_OK || nbands == 1) return st;
