@@ -72,12 +72,41 @@ __device__ __forceinline__ void scan_segments(const float4 (&buf)[kBatch], int n
     }
 }
 
-// PIPELINED (rows of 512..1024 floats, one row per warp): a lane keeps a whole row of 128-bit loads
+// Halves of the register batch, for rows of at most 512 floats: a warp then keeps two rows in flight.
+__device__ __forceinline__ void load_half(const float4 *row4, int n4, int lane, float4 (&buf)[kBatch], int k0)
+{
+#pragma unroll
+    for (int k = 0; k < kBatch / 2; ++k) {
+        const int j = k * 32 + lane;
+        buf[k0 + k] = j < n4 ? __ldg(row4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+__device__ __forceinline__ void scan_half(const float4 (&buf)[kBatch], int k0, int n4, int lane, int w, float *trow,
+                                          float &running, bool relu)
+{
+#pragma unroll
+    for (int k = 0; k < kBatch / 2; ++k) {
+        if (k * 32 < n4) {
+            float4 v = relu ? relu4(buf[k0 + k]) : buf[k0 + k];
+            v.y += v.x; v.z += v.y; v.w += v.z;
+            const float incl = warp_inclusive_scan(v.w, lane);
+            const float add = running + (incl - v.w);
+            running += __shfl_sync(0xffffffffu, incl, 31);
+            const int c = (k * 32 + lane) << 2;
+            if (c < w) {
+                trow[c + 1] = v.x + add; trow[c + 2] = v.y + add;
+                trow[c + 3] = v.z + add; trow[c + 4] = v.w + add;
+            }
+        }
+    }
+}
+
+// PIPELINED (rows of 512..1024 floats, one row per warp; TWO: rows of 256..512 floats, two rows per warp): a lane keeps a whole row of 128-bit loads
 // in flight and the next tile's row is fetched while the current tile is scanned down its columns
 // and stored, so a CTA always has a full tile of loads outstanding.  Otherwise (short rows, many
 // planes) the kernel stays small in registers and relies on many resident CTAs.
 // BIG: 512 threads per CTA, for launches of at most one CTA per SM (twice the loads in flight)
-template <bool VEC4, bool PIPELINED, bool BIG = false>
+template <bool VEC4, bool PIPELINED, bool BIG = false, bool TWO = false>
 __global__ void __launch_bounds__(BIG ? 2 * kMaxThreads : kMaxThreads)
 integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int plane_h, int w, int tile_rows, bool relu,
                       int band_rows, int nbands, int lpad, int rpad)
@@ -101,8 +130,14 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
     float *dst = out + plane * (int64_t)(plane_h + 1) * pw + (int64_t)band * band_rows * pw;
     const int n4 = w >> 2;
     float4 pre[kBatch];      // dead in the instantiations that are not PIPELINED
-    if (PIPELINED && warp < tile_rows && warp < h)
+    if (PIPELINED && TWO) {
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr)
+            if (2 * warp + rr < tile_rows && 2 * warp + rr < h)
+                load_half(reinterpret_cast<const float4 *>(src + (int64_t)(2 * warp + rr) * w), n4, lane, pre, rr * (kBatch / 2));
+    } else if (PIPELINED && warp < tile_rows && warp < h) {
         load_segments(reinterpret_cast<const float4 *>(src + (int64_t)warp * w), n4, 0, lane, pre);
+    }
 
     for (int c = tid; c < w + rpad; c += kThreads) carry[c] = 0.0f;
     if (band == 0)
@@ -115,7 +150,23 @@ integral_image_kernel(const float *__restrict__ in, float *__restrict__ out, int
         float *t = tile + mis;
 
         // ---- 1. row pass
-        if (PIPELINED) {
+        if (PIPELINED && TWO) {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int i = 2 * warp + rr;
+                if (i < rows) {
+                    float *trow = t + i * pw + lpad;
+                    if (lane == 0) trow[0] = 0.0f;
+                    float running = 0.0f;
+                    scan_half(pre, rr * (kBatch / 2), n4, lane, w, trow, running, relu);
+                    if (lane < lpad) trow[-1 - lane] = 0.0f;
+                    for (int j = lane; j < rpad; j += 32) trow[w + 1 + j] = running;
+                }
+                const int rn = r0 + tile_rows + i;
+                if (i < tile_rows && rn < h)
+                    load_half(reinterpret_cast<const float4 *>(src + (int64_t)rn * w), n4, lane, pre, rr * (kBatch / 2));
+            }
+        } else if (PIPELINED) {
             if (warp < rows) {
                 float *trow = t + warp * pw + lpad;
                 if (lane == 0) trow[0] = 0.0f;
@@ -370,19 +421,22 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
     int tile_rows = 9000 / pw;
     // with at most one CTA per SM a CTA of twice the size keeps twice the loads in flight
     const int threads = planes * nbands <= 148 ? 2 * kMaxThreads : kMaxThreads;
-    const bool pipelined = vec4 && w >= 512 && w <= 128 * kBatch && band_rows >= 2 * (threads / 32);
-    if (pipelined) tile_rows = threads / 32;
+    const bool two = vec4 && w >= 256 && w <= 64 * kBatch && band_rows >= 4 * (threads / 32);      // two rows per warp
+    const bool pipelined = two || (vec4 && w >= 512 && w <= 128 * kBatch && band_rows >= 2 * (threads / 32));
+    if (pipelined) tile_rows = (two ? 2 : 1) * (threads / 32);
     if (tile_rows < 1) tile_rows = 1;
     if (tile_rows > band_rows) tile_rows = band_rows > 0 ? band_rows : 1;
     const size_t smem = tile_smem_bytes(tile_rows, w, lpad, rpad);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
     void (*kern)(const float *, float *, int, int, int, bool, int, int, int, int);
     if (threads > kMaxThreads)
-        kern = pipelined ? integral_image_kernel<true, true, true>
-                         : (vec4 ? integral_image_kernel<true, false, true> : integral_image_kernel<false, false, true>);
+        kern = two ? integral_image_kernel<true, true, true, true>
+                   : (pipelined ? integral_image_kernel<true, true, true>
+                                : (vec4 ? integral_image_kernel<true, false, true> : integral_image_kernel<false, false, true>));
     else
-        kern = pipelined ? integral_image_kernel<true, true>
-                         : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>);
+        kern = two ? integral_image_kernel<true, true, false, true>
+                   : (pipelined ? integral_image_kernel<true, true>
+                                : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>));
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("integral_image: shared memory opt-in");
