@@ -67,11 +67,11 @@ BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds t
 # DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
 # profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
 NCU_TRAFFIC = {
-    # profiles/plane_kernels_cfg2_ncu_full.md: 83.93 MB read + 3.82 MB written on cfg2 (4 194 304 input
+    # profiles/plane_kernels_cfg2_ncu_full.md: 83.93 MB read + 4.00 MB written on cfg2 (4 194 304 input
     # elements); below the 100.7 MB algorithmic figure because the 126 MB L2 still holds part of the
     # 16.8 MB grad_input when the kernel ends
-    "backward_plane_kernel": (87.76e6, 4194304),
-    "forward_plane_kernel": (25.99e6, 4194304),
+    "backward_plane_kernel": (87.93e6, 4194304),
+    "forward_plane_kernel": (25.81e6, 4194304),
 }
 
 
