@@ -715,7 +715,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=8)
-    ap.add_argument("--e2e-depth", type=int, default=3, help="batches in flight in the end-to-end leg")
+    ap.add_argument("--e2e-depth", type=int, default=2, help="batches in flight in the end-to-end leg")
     ap.add_argument("--max-seconds", type=int, default=600, help="host-side watchdog for the whole run")
     args = ap.parse_args()
     arm_watchdog(args.max_seconds)
