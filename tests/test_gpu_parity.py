@@ -311,6 +311,23 @@ def test_adjointness_and_linearity_full_size(bc, cfg):
     assert torch.equal(g1, x.grad)
 
 
+def test_batch_shards_reproduce_the_full_batch(bc):
+    """What data-parallel ranks compute: outputs and grad-input of a shard are bitwise the slices of
+    the full-batch result, and the shards' parameter gradients add up to the full-batch gradient."""
+    wl = make_workload("cfg2", batch=8, planes=8)
+    full_out, full_gin, full_gps, _ = run_module(bc, wl.x, wl.stored, wl.grad_output, wl.max_h, wl.max_w, 8, True, True)
+    sums = [np.zeros_like(g, dtype=np.float64) for g in full_gps]
+    for lo, hi in ((0, 3), (3, 8)):                     # uneven shards
+        out, gin, gps, _ = run_module(bc, wl.x[lo:hi], wl.stored, wl.grad_output[lo:hi], wl.max_h, wl.max_w, 8,
+                                      True, True)
+        assert np.array_equal(out, full_out[lo:hi])
+        assert np.array_equal(gin, full_gin[lo:hi])
+        for s, g in zip(sums, gps):
+            s += g
+    for s, g in zip(sums, full_gps):
+        assert max_rel(s, g) < 1e-5
+
+
 def test_parameter_gradients_match_finite_differences(bc):
     """The method of the reference's own test (box_convolution/test.py:276-309): central
     differences of the loss w.r.t. each stored parameter, on a small smooth case."""
