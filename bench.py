@@ -67,7 +67,7 @@ BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds t
 # DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
 # profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
 NCU_TRAFFIC = {
-    # profiles/plane_kernels_cfg2_ncu_full.md: 83.93 MB read + 4.00 MB written on cfg2 (4 194 304 input
+    # ncu capture of the plane kernels on cfg2 (summary under profiles/): 83.93 MB read + 4.00 MB written on cfg2 (4 194 304 input
     # elements); below the 100.7 MB algorithmic figure because the 126 MB L2 still holds part of the
     # 16.8 MB grad_input when the kernel ends
     "backward_plane_kernel": (87.93e6, 4194304),
@@ -443,7 +443,7 @@ def run_integral(args, rank, world, local_rank):
                        "l2": "4.3 GB touched per launch"},
             "roofline": {"bound": "hbm", "kernel": "integral_image_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
-                         # profiles/integral_image_kernel_cfg4_ncu.md: 2.148 GB read + 2.108 GB written
+                         # ncu capture of the integral image kernel on cfg4 (summary under profiles/): 2.148 GB read + 2.108 GB written
                          "traffic": 4.2556e9, "algorithmic_bytes": alg,
                          "mean_us": ms * 1e3, "peak_source": peak_src},
             "cpu_baseline": cpu_baseline, "gpu_launches": args.steps}), flush=True)
