@@ -212,3 +212,15 @@ def test_reference_style_random_cases_fp32():
         want_gin, = torch.autograd.grad(want, xd, go.double())
         assert torch.allclose(y.detach().double(), want.detach(), rtol=3e-5, atol=1e-5), case
         assert torch.allclose(x.grad.double(), want_gin, rtol=3e-5, atol=1e-5), case
+
+
+def test_package_self_test_runs():
+    """`python -m box_convolution.test`, the command the reference documents for its own test file."""
+    import os
+    import subprocess
+    import sys
+    from conftest import PKG_DIR
+    env = dict(os.environ, PYTHONPATH=PKG_DIR + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-m", "box_convolution.test"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "test_box_convolution_module OK" in r.stdout
