@@ -62,6 +62,35 @@ struct LaunchScope {
     int slot;
 };
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// launch_overlapped() lets the GPU schedule a kernel's CTAs while the kernel in front of it in the
+// stream is still running; such a kernel must call grid_dependency_wait() before it touches
+// anything a predecessor in the stream may still be writing or reading (the wait returns when the
+// kernel in front has completed and flushed, which in turn had waited for the one before it).
+// What overlaps is launch latency and the instructions before the wait.
+// grid_dependency_release() in the kernel in front allows the scheduling to begin before it exits.
+#if defined(__CUDACC__)
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                                     cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // ---- launchers (one per translation unit) --------------------------------------------------
 // (the general kernels exist for float and double; everything else is float only)
 template <typename T>

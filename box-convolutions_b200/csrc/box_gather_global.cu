@@ -268,6 +268,7 @@ __global__ void finish_param_grads_kernel(const T *__restrict__ partials, BoxPar
                                           int per_box, bool normalize, bool exact, T rep_h, T rep_w,
                                           int need_mask, T *__restrict__ grad_params)
 {
+    grid_dependency_wait();
     const int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (k >= count) return;
@@ -299,8 +300,9 @@ int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int co
     const int blocks = (count + warps_per_block - 1) / warps_per_block;
     {
         LaunchScope scope(KID_FINISH_PARAM_GRADS, s);
-        finish_param_grads_kernel<T><<<blocks, warps_per_block * 32, 0, s>>>(
-            partials, bp, count, per_box, normalize, exact, rep_h, rep_w, need_mask, grad_params);
+        if (launch_overlapped(finish_param_grads_kernel<T>, (unsigned)blocks, warps_per_block * 32, 0, s, partials, bp,
+                              count, per_box, normalize, exact, rep_h, rep_w, need_mask, grad_params) != cudaSuccess)
+            return check_launch("finish_param_grads");
     }
     return check_launch("finish_param_grads");
 }

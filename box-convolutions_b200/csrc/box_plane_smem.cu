@@ -299,6 +299,7 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *out, int 
     float *sRow = sI + layout_floats(h, w);
     float *sCol = sRow + g.ntiles * kTile;
     __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
+    grid_dependency_release();
 
     const int64_t nc = blockIdx.x / fsplit;
     const int part = blockIdx.x % fsplit;
@@ -311,13 +312,16 @@ forward_plane_kernel(const float *__restrict__ x, BoxParams bp, float *out, int 
     Strip st[T];
 #pragma unroll
     for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
+    init_integral_padding(sI, g);
 
+    // everything above touches registers and shared memory only; from here on the parameters and
+    // the input are read, which the kernel in front of this one in the stream may have written
+    grid_dependency_wait();
     if ((int)threadIdx.x < f_end - f_begin) {
         const Box box = load_box(bp, c * F + f_begin + threadIdx.x);
         store_taps(sTaps + threadIdx.x * kTapWords,
                    taps_forward(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
     }
-    init_integral_padding(sI, g);
     {
         Blocks<T> blk;
         build_rows<T, FAST, false, FUSED>(blk, st, x + nc * (int64_t)h * w, 0u, sRow, g, cg, rg, FUSED && fu.input_relu);
@@ -417,6 +421,7 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
     __shared__ __align__(16) float sTaps[kMaxFilters * kTapWords];
     __shared__ float red[16][kNumSums];
     __shared__ __align__(8) unsigned long long mbar[2];
+    grid_dependency_release();
 
     const int64_t nc = blockIdx.x;
     const int c = (int)(nc % C), n = (int)(nc / C);
@@ -437,11 +442,15 @@ backward_plane_kernel(const float *__restrict__ x, const float *__restrict__ gra
         mbar_init(mbarG, 1);
         fence_mbar_init();
     }
+    init_integral_padding(sI, g);
+
+    // registers and shared memory only up to here; now global memory that the kernel in front of
+    // this one in the stream may still be using
+    grid_dependency_wait();
     if (tid < F) {
         const Box box = load_box(bp, c * F + tid);
         store_taps(sTaps + tid * kTapWords, taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
     }
-    init_integral_padding(sI, g);
     if (STAGED) {
         __syncthreads();                                   // barriers initialised before anyone waits
         if (tid == 0) {
@@ -682,8 +691,9 @@ static int launch_forward_plane_impl(const float *x, const BoxParams &bp, const 
     const Fusion none{0, nullptr, nullptr, nullptr, 0};
     {
         LaunchScope scope(KID_FORWARD_PLANE, s);
-        kern<<<(unsigned)(planes * fsplit), warps * 32, smem, s>>>(x, bp, out, C, F, h, w, fsplit, normalize, exact,
-                                                                  fu ? *fu : none);
+        if (launch_overlapped(kern, (unsigned)(planes * fsplit), warps * 32, smem, s, x, bp, out, C, F, h, w, fsplit,
+                              normalize, exact, fu ? *fu : none) != cudaSuccess)
+            return check_launch("forward_plane");
     }
     return check_launch("forward_plane");
 }
@@ -740,8 +750,9 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     if (st != BC_OK) return st;
     {
         LaunchScope scope(KID_BACKWARD_PLANE, s);
-        kern<<<(unsigned)planes, warps * 32, smem, s>>>(x, grad_output, bp, grad_input, partials, N, C, F, h, w,
-                                                       normalize, exact, write_gin);
+        if (launch_overlapped(kern, (unsigned)planes, warps * 32, smem, s, x, grad_output, bp, grad_input, partials, N,
+                              C, F, h, w, normalize, exact, write_gin) != cudaSuccess)
+            return check_launch("backward_plane");
     }
     st = check_launch("backward_plane");
     if (st != BC_OK || !need_params) return st;

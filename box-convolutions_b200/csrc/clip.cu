@@ -28,6 +28,7 @@ template <typename T>
 __global__ void clip_kernel(T *x_min, T *x_max, T *y_min, T *y_max, int count,
                             double inv_rep_h, double inv_rep_w, double min_size, double max_h, double max_w)
 {
+    grid_dependency_release();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) {
         clip_pair(x_min + i, x_max + i, inv_rep_h, min_size, max_h);
