@@ -513,7 +513,7 @@ def run_ours(args, rank, world, local_rank):
 
     # The graphs hold the compute of a step (clip, forward, backward); the all-reduce of the packed
     # parameter gradient is issued after each replay on the same stream, outside the graph.
-    graphs, packed = None, []
+    graphs, packed, multi = None, [], None
     if not args.no_graph:
         stage("capturing %d CUDA graphs" % BUFFER_SETS)
         graphs, keep = [], []
@@ -531,6 +531,16 @@ def run_ours(args, rank, world, local_rank):
         for s in range(BUFFER_SETS):
             graphs[s].replay()
         torch.cuda.synchronize()
+        if world == 1:
+            # one more graph that runs a step on every buffer set in turn: BUFFER_SETS steps per launch
+            multi = torch.cuda.CUDAGraph()
+            for p in params:
+                p.grad = None
+            with torch.cuda.graph(multi, pool=pool):
+                for s in range(BUFFER_SETS):
+                    keep.append(compute(s))
+            multi.replay()
+            torch.cuda.synchronize()
 
     # With graphs, the all-reduce of step k runs on a side stream while step k+1 computes (the way a
     # trainer overlaps gradient reduction with the rest of the backward pass); a buffer set is not
@@ -540,7 +550,12 @@ def run_ours(args, rank, world, local_rank):
 
     def run_steps(k):
         main = torch.cuda.current_stream()
-        for i in range(k):
+        done = 0
+        if multi is not None:
+            for _ in range(k // BUFFER_SETS):
+                multi.replay()
+            done = (k // BUFFER_SETS) * BUFFER_SETS
+        for i in range(done, k):
             s = i % BUFFER_SETS
             if graphs is not None:
                 if reduced[s] is not None:
@@ -690,7 +705,10 @@ def run_ours(args, rank, world, local_rank):
             "config": {"workload": describe(args.workload), "global_batch": N * world, "batch_per_gpu": N,
                        "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (
                            BUFFER_SETS, wl.algorithmic_bytes / 1e6),
-                       "launch": "eager" if graphs is None else "cuda graph replay of clip+forward+backward, one graph per buffer set" + ("; all-reduce of step k on a side stream, overlapping step k+1" if world > 1 else ""),
+                       "launch": "eager" if graphs is None else (
+                           "cuda graph replay of clip+forward+backward, %d consecutive steps (one per buffer set) per graph launch" % BUFFER_SETS
+                           if multi is not None else
+                           "cuda graph replay of clip+forward+backward, one graph per buffer set; all-reduce of step k on a side stream, overlapping step k+1"),
                        "eager_ms_per_step": eager_ms,
                        "collective": "nccl all_reduce of the packed (4,C,F) parameter gradient" if world > 1 else "none"},
             "hbm_gbs_step": wl.algorithmic_bytes * world / (ms_per_step * 1e-3) / 1e9,
