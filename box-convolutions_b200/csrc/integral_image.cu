@@ -352,11 +352,18 @@ __global__ void band_last_rows_kernel(float *__restrict__ out, int64_t planes, i
     const int64_t plane = i / ncols;
     const int c = c0 + (int)(i - plane * ncols);
     float *base = out + plane * (int64_t)(plane_h + 1) * pw + c;
+    const int64_t stride = (int64_t)band_rows * pw;
     float run = 0.0f;
-    for (int k = 1; k < nbands; ++k) {
-        const float v = base[(int64_t)k * band_rows * pw];
-        base[(int64_t)k * band_rows * pw] = v + run;
-        run += v;
+    // 16 rows at a time: the loads are independent of one another, only the sums are a chain
+    for (int k0 = 1; k0 < nbands; k0 += 16) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = k0 + j < nbands ? base[(k0 + j) * stride] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (k0 + j < nbands) base[(k0 + j) * stride] = v[j] + run;
+            run += v[j];
+        }
     }
 }
 
