@@ -1,23 +1,33 @@
 #!/usr/bin/env python
 """Benchmark of the BoxConv2d forward+backward hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg5]
 
-(`--workload cfg4` times the integral image alone, `--workload infer` the batch-1 inference block
-tails of one frame; the default and the contract line are cfg2.)
+The default workload and the contract line are cfg5: the 1/8-frame ENet box block,
+BoxConv2d(32, 4, 64, 128), on a GLOBAL batch of 256 samples that is divided over the GPUs (strong
+scaling: 256 / 128 / 64 / 32 samples per GPU on 1 / 2 / 4 / 8 GPUs).  The line also carries a `cfg2`
+key: the same block at 16 samples per GPU.  `--workload cfg2|cfg3|cfg1` time those shapes per GPU
+(weak scaling), `--workload cfg4` the integral image alone, `--workload infer` the batch-1 inference
+block tails of one frame.
 
 One step = one training pass of the box block over one batch of synthetic input: parameter
 clip, forward, backward (grad-input and the four parameter gradients) and, on more than one GPU,
-the all-reduce of the packed (4, C, F) parameter gradient.  Each rank works on its own batch of
-the per-GPU shape (weak scaling); `value` is the whole job's output elements per second.
+the all-reduce of the packed (4, C, F) parameter gradient.  `value` is the whole job's output
+elements per second: the median of at least 15 consecutive rounds of K steps (enough rounds for a
+timed region of 0.3 s), each round between two CUDA events, per round the maximum over the ranks.
+Every GPU count launches the same way: one CUDA graph replay per step.
 
 The line printed by rank 0 carries, besides the contract keys:
   roofline      achieved HBM GB/s of the dominant kernel (algorithmic bytes / mean device time of
                 that kernel, from per-kernel CUDA events recorded by the library during an eager
-                repeat of the timed steps) against the measured copy bandwidth of this pool
+                repeat of K steps) against the measured copy bandwidth of this pool
   cpu_baseline  the reference's own CPU code on this machine's host cores (N=1 only)
-  e2e           the same metric from pinned host buffers to host results through the module
-  clocks        SM clock and throttle reasons sampled through NVML while the GPU was busy
+  e2e           the same metric from pinned host buffers to host results through the module, and
+                the floor that bare copies of the same bytes set
+  clocks        SM clock and throttle reasons sampled through NVML during the timed rounds
+  allreduce_check  (more than one GPU) the reduced gradients against the sum of the ranks' local
+                gradients and every rank's shard against a full-batch run on rank 0; the run exits
+                non-zero when they differ
 
 `--impl reference` times the reference's CPU implementation of the same step (its compiled
 extension built by oracle/build_ref.py; the plain-C oracle if that build is absent).
@@ -77,6 +87,9 @@ NCU_TRAFFIC = {
 
 def describe(name):
     N, C, F, h, w = CONFIGS[name][:5]
+    if name == "cfg5":
+        return "cfg5: BoxConv2d(%d,%d,%d,%d) fwd+bwd, global batch %d (input %dx%dx%dx%d) divided over the GPUs, fp32, normalize, exact" % (
+            C, F, h, w, N, N, C, h, w)
     return "%s: BoxConv2d(%d,%d,%d,%d) fwd+bwd, input %dx%dx%dx%d per GPU, fp32, normalize, exact" % (
         name, C, F, h, w, N, C, h, w)
 
@@ -88,7 +101,7 @@ def measured_peak():
             return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
         except Exception:
             pass
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s; MEASURED_PEAKS.json is absent)"
 
 
 # ------------------------------------------------------------------------------------------
@@ -146,12 +159,20 @@ def run_reference(args, rank, world):
     sec = sum(times) / len(times)
     value = wl.outputs / sec / 1e9
     sample = "batch %d of %d of %s per step, %d steps, mean" % (n, CONFIGS[args.workload][0], args.workload, args.steps)
+    strong = args.workload == "cfg5"
+    config = training_config(args.workload, args.gpus, strong)
+    config.update({
+        "l2": "host memory: no device buffers",
+        "launch": "host loop over the reference's four extension functions, as its autograd Function calls them",
+        "rounds": 1, "round_ms_min": sec * 1e3 * args.steps, "round_ms_max": sec * 1e3 * args.steps,
+        "timing": "mean host wall time of `steps` steps on a bounded sample of the batch (see cpu_baseline.sample)",
+        "eager_ms_per_step": sec * 1e3, "collective": "none",
+        "host_threads": ref.cores, "os_cpu_count": os.cpu_count()})
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": describe(args.workload), "host_threads": ref.cores,
-                   "os_cpu_count": os.cpu_count()},
+        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -371,10 +392,12 @@ class ClockSampler(threading.Thread):
         0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting",
     }
 
-    def __init__(self, index):
+    def __init__(self, index, active=True, period_s=0.02):
         super().__init__(daemon=True)
         self.samples = []      # (time, sm_mhz, reasons_bitmask, power_w)
         self.stop_flag = False
+        self.active = active   # NVML is only called while this is set (its calls contend with kernel launches)
+        self.period_s = period_s
         self.ok = False
         try:
             import pynvml
@@ -391,6 +414,9 @@ class ClockSampler(threading.Thread):
             return
         nv = self.nv
         while not self.stop_flag:
+            if not self.active:
+                time.sleep(self.period_s)
+                continue
             try:
                 mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
                 try:
@@ -401,7 +427,7 @@ class ClockSampler(threading.Thread):
                 self.samples.append((time.perf_counter(), mhz, rs, pw))
             except Exception:
                 pass
-            time.sleep(0.002)
+            time.sleep(self.period_s)
 
     def summary(self, t0, t1):
         sel = [s for s in self.samples if t0 <= s[0] <= t1]
@@ -494,204 +520,304 @@ def run_integral(args, rank, world, local_rank):
             "cpu_baseline": cpu_baseline, "gpu_launches": args.steps}), flush=True)
 
 
-def run_ours(args, rank, world, local_rank):
-    import torch.distributed as dist
-    import box_convolution as bc
-    from box_convolution import _cabi
+class TrainingRun:
+    """One workload on this rank: module, rotating buffer sets, one CUDA graph per buffer set holding
+    the compute of a step (clip, forward, backward, finishing kernel)."""
 
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    def __init__(self, args, name, rank, world, dev):
+        import box_convolution as bc
+        from box_convolution import _cabi
+        self.bc, self.cabi = bc, _cabi
+        self.args, self.name, self.rank, self.world, self.dev = args, name, rank, world, dev
+        # cfg5 is the batch-sharded configuration: a global batch of 256 divided over the ranks (strong
+        # scaling); every other workload is run once per rank (weak scaling)
+        self.strong = name == "cfg5"
+        full_n = CONFIGS[name][0]
+        if self.strong and full_n % world:
+            raise SystemExit("cfg5: the global batch of %d does not divide over %d GPUs" % (full_n, world))
+        # the host copy of the workload feeds buffer set 0 of rank 0, the end-to-end leg and the CPU baseline
+        self.wl = wl = make_workload(name, batch=full_n // world if self.strong else None)
+        N, C, F, h, w = wl.shape
+        self.module = m = bc.BoxConv2d(C, F, wl.max_h, wl.max_w, reparametrization_factor=8, normalize=True).to(dev)
+        with torch.no_grad():
+            for p, v in zip((m.x_min, m.x_max, m.y_min, m.y_max), wl.stored):
+                p.copy_(torch.from_numpy(v))
+        m.train()
+        self.params = [m.x_min, m.x_max, m.y_min, m.y_max]
+        # distinct inputs per rank and per buffer set (same distribution)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1234 + rank)
+        self.xs, self.gos = [], []
+        for s in range(BUFFER_SETS):
+            if s == 0 and rank == 0:
+                self.xs.append(torch.from_numpy(wl.x).to(dev).requires_grad_())
+                self.gos.append(torch.from_numpy(wl.grad_output).to(dev))
+            else:
+                self.xs.append(torch.randn((N, C, h, w), device=dev, generator=gen).requires_grad_())
+                self.gos.append(torch.randn((N, C * F, h, w), device=dev, generator=gen))
+        self.graphs, self.outs, self.packed = None, [], []
+        self.works = [None] * BUFFER_SETS
+        self.step_index = 0
 
-    stage("process group ready (world %d)" % world)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-
-    # cfg5 is the batch-sharded configuration: a global batch of 256 divided over the ranks (strong
-    # scaling); every other workload is run once per rank (weak scaling)
-    strong = args.workload == "cfg5"
-    wl = make_workload(args.workload, batch=CONFIGS[args.workload][0] // world if strong else None)
-    N, C, F, h, w = wl.shape
-    module = bc.BoxConv2d(C, F, wl.max_h, wl.max_w, reparametrization_factor=8, normalize=True).to(dev)
-    with torch.no_grad():
-        for p, v in zip((module.x_min, module.x_max, module.y_min, module.y_max), wl.stored):
-            p.copy_(torch.from_numpy(v))
-    module.train()
-    params = [module.x_min, module.x_max, module.y_min, module.y_max]
-
-    # distinct inputs per rank and per buffer set (same distribution)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(1234 + rank)
-    xs, gos = [], []
-    for s in range(BUFFER_SETS):
-        if s == 0 and rank == 0:
-            xs.append(torch.from_numpy(wl.x).to(dev).requires_grad_())
-            gos.append(torch.from_numpy(wl.grad_output).to(dev))
-        else:
-            xs.append(torch.randn((N, C, h, w), device=dev, generator=gen).requires_grad_())
-            gos.append(torch.randn((N, C * F, h, w), device=dev, generator=gen))
-
-    def compute(s):
-        for p in params:
+    def compute(self, s):
+        for p in self.params:
             p.grad = None
-        xs[s].grad = None
-        out = module(xs[s])
-        out.backward(gos[s])
+        self.xs[s].grad = None
+        out = self.module(self.xs[s])
+        out.backward(self.gos[s])
         return out
 
-    def step(s):
-        out = compute(s)
-        if world > 1:
-            bc.allreduce_box_gradients(module)
+    def eager_step(self, s):
+        out = self.compute(s)
+        if self.world > 1:
+            self.bc.allreduce_box_gradients(self.module)
         return out
 
-    stage("eager warm-up")
-    # ---- warm-up (eager), then capture one CUDA graph per buffer set
-    for i in range(max(args.warmup, 3)):
-        step(i % BUFFER_SETS)
-    torch.cuda.synchronize()
-    launches_before = _cabi.lib.bc_launch_count()
-    step(0)
-    launches_per_step = _cabi.lib.bc_launch_count() - launches_before
-    torch.cuda.synchronize()
-
-    # The graphs hold the compute of a step (clip, forward, backward); the all-reduce of the packed
-    # parameter gradient is issued after each replay on the same stream, outside the graph.
-    graphs, packed, multi = None, [], None
-    if not args.no_graph:
-        stage("capturing %d CUDA graphs" % BUFFER_SETS)
-        graphs, keep = [], []
-        pool = None
+    def warm_up_and_capture(self):
+        import torch.distributed as dist
+        for i in range(max(self.args.warmup, 3)):
+            self.eager_step(i % BUFFER_SETS)
+        torch.cuda.synchronize()
+        before = self.cabi.lib.bc_launch_count()
+        self.compute(0)
+        self.launches_per_step = self.cabi.lib.bc_launch_count() - before
+        torch.cuda.synchronize()
+        if self.args.no_graph:
+            return
+        self.graphs, pool = [], None
         for s in range(BUFFER_SETS):
             g = torch.cuda.CUDAGraph()
-            for p in params:
+            for p in self.params:
                 p.grad = None
-            xs[s].grad = None
+            self.xs[s].grad = None
             with torch.cuda.graph(g, pool=pool):
-                keep.append(compute(s))
-                packed.append(bc.packed_box_gradient(module)[0])
+                self.outs.append(self.compute(s))
+                self.packed.append(self.bc.packed_box_gradient(self.module)[0])
             pool = g.pool()
-            graphs.append(g)
-        for s in range(BUFFER_SETS):
-            graphs[s].replay()
+            self.graphs.append(g)
+        for g in self.graphs:
+            g.replay()
         torch.cuda.synchronize()
-        if world == 1:
-            # one more graph that runs a step on every buffer set in turn: BUFFER_SETS steps per launch
-            multi = torch.cuda.CUDAGraph()
-            for p in params:
-                p.grad = None
-            with torch.cuda.graph(multi, pool=pool):
-                for s in range(BUFFER_SETS):
-                    keep.append(compute(s))
-            multi.replay()
+        if self.world > 1:
+            for s in range(BUFFER_SETS):        # the communicator's first collectives, outside any timing
+                dist.all_reduce(self.packed[s])
             torch.cuda.synchronize()
 
-    # With graphs, the all-reduce of step k runs on a side stream while step k+1 computes (the way a
-    # trainer overlaps gradient reduction with the rest of the backward pass); a buffer set is not
-    # reused before its reduction has finished, and the timed region ends only when all are done.
-    comm_stream = torch.cuda.Stream(dev) if world > 1 else None
-    reduced = [None] * BUFFER_SETS
+    def run_steps(self, k):
+        """k consecutive steps, the same way at every GPU count: one graph replay per step; with more than
+        one GPU the all-reduce of the step's packed gradient is issued right behind it (asynchronously:
+        it runs on the process group's own stream, under the kernels of the next step).  A buffer set is
+        not replayed again before its previous reduction has finished (a stream-side wait)."""
+        import torch.distributed as dist
+        for _ in range(k):
+            s = self.step_index % BUFFER_SETS
+            self.step_index += 1
+            if self.graphs is None:
+                self.eager_step(s)
+                continue
+            if self.works[s] is not None:
+                self.works[s].wait()
+                self.works[s] = None
+            self.graphs[s].replay()
+            if self.world > 1:
+                self.works[s] = dist.all_reduce(self.packed[s], async_op=True)
 
-    def run_steps(k):
-        main = torch.cuda.current_stream()
-        done = 0
-        if multi is not None:
-            for _ in range(k // BUFFER_SETS):
-                multi.replay()
-            done = (k // BUFFER_SETS) * BUFFER_SETS
-        for i in range(done, k):
-            s = i % BUFFER_SETS
-            if graphs is not None:
-                if reduced[s] is not None:
-                    main.wait_event(reduced[s])
-                graphs[s].replay()
-                if world > 1:
-                    ready = torch.cuda.Event()
-                    ready.record(main)
-                    with torch.cuda.stream(comm_stream):
-                        comm_stream.wait_event(ready)
-                        dist.all_reduce(packed[s])
-                        reduced[s] = torch.cuda.Event()
-                        reduced[s].record(comm_stream)
+    def replay_only_ms_per_step(self, rounds=8):
+        """The same graph replays without the all-reduce behind them (median of a few rounds, max over
+        ranks): what the step costs before any communication is added."""
+        import torch.distributed as dist
+        if self.graphs is None:
+            return None
+        K = self.args.steps
+        self.drain()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
+        events[0].record()
+        for r in range(rounds):
+            for i in range(K):
+                self.graphs[i % BUFFER_SETS].replay()
+            events[r + 1].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([events[r].elapsed_time(events[r + 1]) for r in range(rounds)], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return statistics.median(t.tolist()) / K
+
+    def drain(self):
+        for s in range(BUFFER_SETS):
+            if self.works[s] is not None:
+                self.works[s].wait()
+                self.works[s] = None
+
+    def timed_rounds(self, sampler):
+        """R consecutive rounds of K steps, one CUDA event between rounds; returns the per-round times
+        (ms, max over ranks) and the host-clock window of the timed region."""
+        import torch.distributed as dist
+        K = self.args.steps
+        self.run_steps(max(self.args.warmup, 3))
+        self.drain()
+        torch.cuda.synchronize()
+        # pilot round: how many rounds make the timed region long enough for clock sampling
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        self.run_steps(K)
+        self.drain()
+        p1.record()
+        torch.cuda.synchronize()
+        pilot = torch.tensor([p0.elapsed_time(p1)], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(pilot, op=dist.ReduceOp.MAX)
+        rounds = self.args.rounds or int(min(1000, max(15, -(-self.args.min_timed_ms // max(float(pilot.item()), 1e-3)))))
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        if sampler is not None:
+            sampler.active = True
+        t_start = time.perf_counter()
+        events[0].record()
+        for r in range(rounds):
+            self.run_steps(K)
+            if r == rounds - 1:
+                self.drain()                    # the region ends when the last reduction has finished
+            events[r + 1].record()
+        torch.cuda.synchronize()
+        t_end = time.perf_counter()
+        if sampler is not None:
+            sampler.active = False
+        if self.world > 1:
+            dist.barrier()
+        per_round = torch.tensor([events[r].elapsed_time(events[r + 1]) for r in range(rounds)],
+                                 device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(per_round, op=dist.ReduceOp.MAX)
+        return per_round.tolist(), (t_start, t_end)
+
+    def per_kernel(self):
+        """Device time of every kernel of the step, from the library's own event pairs around each
+        launch, over an eager repeat of K steps (events cannot be read back from a replayed graph)."""
+        import ctypes
+        lib, K = self.cabi.lib, self.args.steps
+        self.cabi.check(lib.bc_profile_start(K * max(self.launches_per_step, 1) + 16), "bc_profile_start")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            self.eager_step(i % BUFFER_SETS)
+        e1.record()
+        torch.cuda.synchronize()
+        lib.bc_profile_stop()
+        eager_ms = e0.elapsed_time(e1) / K
+        per = {}
+        kid, ms = ctypes.c_int(), ctypes.c_float()
+        for i in range(lib.bc_profile_count()):
+            self.cabi.check(lib.bc_profile_get(i, ctypes.byref(kid), ctypes.byref(ms)), "bc_profile_get")
+            per.setdefault(lib.bc_kernel_name(kid.value).decode(), []).append(ms.value)
+        kernels = {k: {"launches": len(v), "mean_us": 1e3 * sum(v) / len(v), "total_ms": sum(v)} for k, v in per.items()}
+        roofline = None
+        if kernels:
+            N, C, F, h, w = self.wl.shape
+            top = max(kernels, key=lambda k: kernels[k]["total_ms"])
+            alg = kernel_algorithmic_bytes(top, N, C, F, h, w)
+            peak, peak_src = measured_peak()
+            if alg is not None:
+                achieved = alg / (kernels[top]["mean_us"] * 1e-6) / 1e9
+                traffic = None
+                if top in NCU_TRAFFIC:
+                    b, units = NCU_TRAFFIC[top]
+                    traffic = b * (N * C * h * w) / units
+                roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                            "frac": achieved / peak, "traffic": traffic,
+                            "traffic_source": None if traffic is None else
+                            "ncu capture of an earlier run of this kernel (summary under profiles/), scaled by the elements per launch; a constant, not measured by this run",
+                            "algorithmic_bytes": alg, "mean_us": kernels[top]["mean_us"], "peak_source": peak_src,
+                            "kernels": {k: round(v["mean_us"], 2) for k, v in kernels.items()}}
+        return roofline, eager_ms
+
+    def check_sharding(self):
+        """On more than one GPU, outside any timing: (1) the all-reduced packed gradient of every buffer
+        set equals the sum of the ranks' local gradients; (2) rank 0 recomputes the whole global batch of
+        buffer set 0 from the ranks' inputs and compares every rank's output and grad-input shard with its
+        slice, and the reduced parameter gradient with the full-batch one."""
+        import torch.distributed as dist
+        world, rank, dev = self.world, self.rank, self.dev
+        self.drain()
+        torch.cuda.synchronize()
+        worst = {"allreduce_vs_sum_of_locals": 0.0, "output_shard_vs_full_batch": 0.0,
+                 "grad_input_shard_vs_full_batch": 0.0, "reduced_grad_vs_full_batch": 0.0}
+
+        def rel(a, b):
+            return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+        local0 = None
+        for s in range(BUFFER_SETS):
+            if self.graphs is not None:
+                self.graphs[s].replay()
+                packed = self.packed[s]
             else:
-                step(s)
-        if comm_stream is not None:
-            main.wait_stream(comm_stream)
+                self.compute(s)
+                packed = self.bc.packed_box_gradient(self.module)[0]
+            local = packed.clone()
+            gathered = [torch.empty_like(local) for _ in range(world)]
+            dist.all_gather(gathered, local)
+            dist.all_reduce(packed)
+            want = torch.stack(gathered).double().sum(0)
+            worst["allreduce_vs_sum_of_locals"] = max(worst["allreduce_vs_sum_of_locals"], rel(packed, want))
+            if s == 0:
+                local0 = (packed.clone(), self.outs[0].detach().clone() if self.graphs is not None else None,
+                          self.xs[0].grad.detach().clone())
+        # (2) the global batch on rank 0
+        N, C, F, h, w = self.wl.shape
+        reduced, out_shard, gin_shard = local0
+        if out_shard is None:
+            out_shard = self.compute(0).detach().clone()
+            gin_shard = self.xs[0].grad.detach().clone()
 
-    # ---- the timed region
-    stage("timed region: %d steps" % args.steps)
-    run_steps(max(args.warmup, 3))
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_start = time.perf_counter()
-    ev0.record()
-    run_steps(args.steps)
-    ev1.record()
-    torch.cuda.synchronize()
-    t_end = time.perf_counter()
-    if world > 1:
-        dist.barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_per_step = ms_total / args.steps
-    value = wl.outputs * world / (ms_per_step * 1e-3) / 1e9
+        def gather_all(t):
+            full = torch.empty((world * t.shape[0],) + tuple(t.shape[1:]), device=dev, dtype=t.dtype)
+            dist.all_gather_into_tensor(full, t.contiguous())
+            return full
 
-    stage("eager repeat with per-kernel events")
-    # ---- per-kernel device times: the same steps, eagerly, with the library's event pairs
-    roofline = None
-    eager_ms = None
-    _cabi.check(_cabi.lib.bc_profile_start(args.steps * max(launches_per_step, 1) + 16), "bc_profile_start")
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i % BUFFER_SETS)
-    e1.record()
-    torch.cuda.synchronize()
-    _cabi.lib.bc_profile_stop()
-    t_busy_end = time.perf_counter()
-    eager_ms = e0.elapsed_time(e1) / args.steps
-    import ctypes
-    per_kernel = {}
-    kid, ms = ctypes.c_int(), ctypes.c_float()
-    for i in range(_cabi.lib.bc_profile_count()):
-        _cabi.check(_cabi.lib.bc_profile_get(i, ctypes.byref(kid), ctypes.byref(ms)), "bc_profile_get")
-        per_kernel.setdefault(_cabi.lib.bc_kernel_name(kid.value).decode(), []).append(ms.value)
-    kernels = {k: {"launches": len(v), "mean_us": 1e3 * sum(v) / len(v), "total_ms": sum(v)} for k, v in per_kernel.items()}
-    if kernels:
-        top = max(kernels, key=lambda k: kernels[k]["total_ms"])
-        alg = kernel_algorithmic_bytes(top, N, C, F, h, w)
-        peak, peak_src = measured_peak()
-        if alg is not None:
-            achieved = alg / (kernels[top]["mean_us"] * 1e-6) / 1e9
-            traffic = None
-            if top in NCU_TRAFFIC:
-                b, units = NCU_TRAFFIC[top]
-                traffic = b * (N * C * h * w) / units
-            roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": traffic, "algorithmic_bytes": alg,
-                        "mean_us": kernels[top]["mean_us"], "peak_source": peak_src,
-                        "kernels": {k: round(v["mean_us"], 2) for k, v in kernels.items()}}
+        x_all, go_all = gather_all(self.xs[0].detach()), gather_all(self.gos[0])
+        out_all, gin_all = gather_all(out_shard), gather_all(gin_shard)
+        if rank == 0:
+            x_all.requires_grad_()
+            for p in self.params:
+                p.grad = None
+            out_full = self.module(x_all)
+            out_full.backward(go_all)
+            full_grad = self.bc.packed_box_gradient(self.module)[0]
+            worst["output_shard_vs_full_batch"] = rel(out_all, out_full.detach())
+            worst["grad_input_shard_vs_full_batch"] = rel(gin_all, x_all.grad)
+            worst["reduced_grad_vs_full_batch"] = rel(reduced, full_grad)
+        verdict = torch.tensor([worst[k] for k in sorted(worst)], device=dev, dtype=torch.float64)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
+        worst = dict(zip(sorted(worst), verdict.tolist()))
+        # sums of identical terms in another order: 1e-5; shards are computed plane by plane by the same
+        # kernels: 1e-6 (expected exactly 0); full-batch gradient against the sum of shard gradients: 1e-3
+        limits = {"allreduce_vs_sum_of_locals": 1e-5, "output_shard_vs_full_batch": 1e-6,
+                  "grad_input_shard_vs_full_batch": 1e-6, "reduced_grad_vs_full_batch": 1e-3}
+        ok = all(worst[k] <= limits[k] for k in worst)
+        del x_all, go_all, out_all, gin_all
+        torch.cuda.empty_cache()
+        return ("ok" if ok else "FAILED"), worst
 
-    # ---- end to end: pinned host buffers in, host results out, through the module
-    e2e = None
-    stage("end-to-end leg")
-    if not args.skip_e2e:
+    def end_to_end(self):
+        """The same step from pinned host buffers to host results through HostPipeline, and the bare
+        bidirectional copies of the same bytes as a floor."""
+        import torch.distributed as dist
+        args, wl, dev, world = self.args, self.wl, self.dev, self.world
+        N, C, F, h, w = wl.shape
         hx = torch.from_numpy(wl.x).pin_memory()
         hgo = torch.from_numpy(wl.grad_output).pin_memory()
         depth = max(1, args.e2e_depth)
-        # batches in flight write to distinct host result buffers
         results = [(torch.empty((N, C * F, h, w), dtype=torch.float32).pin_memory(),
                     torch.empty((N, C, h, w), dtype=torch.float32).pin_memory(),
                     torch.empty((4, C, F), dtype=torch.float32).pin_memory()) for _ in range(depth)]
         hout, hgin, hgp = results[0]
-        pipe = bc.HostPipeline(module, N, h, w, chunks=args.e2e_chunks, depth=depth)
+        pipe = self.bc.HostPipeline(self.module, N, h, w, chunks=args.e2e_chunks, depth=depth)
         k_e2e = max(3, min(args.steps, 20))
         for _ in range(2):
             pipe.step(hx, hgo, hout, hgin, hgp)
@@ -708,29 +834,96 @@ def run_ours(args, rank, world, local_rank):
             pipe.wait(t)
         torch.cuda.synchronize()
         sec = (time.perf_counter() - w0) / k_e2e
+        # floor: the same bytes as plain asynchronous copies, both directions at once, nothing else
+        up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        dx, dgo = torch.empty_like(hx, device=dev), torch.empty_like(hgo, device=dev)
+        dout, dgin = torch.empty_like(hout, device=dev), torch.empty_like(hgin, device=dev)
+        torch.cuda.synchronize()
         if world > 1:
-            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.barrier()
+        f0 = time.perf_counter()
+        for _ in range(k_e2e):
+            with torch.cuda.stream(up):
+                dx.copy_(hx, non_blocking=True)
+                dgo.copy_(hgo, non_blocking=True)
+            with torch.cuda.stream(down):
+                hout.copy_(dout, non_blocking=True)
+                hgin.copy_(dgin, non_blocking=True)
+        torch.cuda.synchronize()
+        floor = (time.perf_counter() - f0) / k_e2e
+        if world > 1:
+            t = torch.tensor([sec, floor], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-        e2e = {"value": wl.outputs * world / sec / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": hx.numel() * 4 + hgo.numel() * 4,
-               "d2h_bytes_per_step": (hout.numel() + hgin.numel() + hgp.numel()) * 4,
-               "ms_per_step": sec * 1e3, "steps": k_e2e, "chunks": args.e2e_chunks, "batches_in_flight": depth,
-               "api": "box_convolution.HostPipeline.submit/wait -> bc_boxconv2d_host_step (C ABI, pinned host buffers in and out, "
-                      "chunked copy/compute overlap on 3 streams; every batch's inputs go up and its results come back inside the timed region)"}
-        t_busy_end = time.perf_counter()
+            sec, floor = (float(v) for v in t.tolist())
+        return {"value": wl.outputs * world / sec / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": hx.numel() * 4 + hgo.numel() * 4,
+                "d2h_bytes_per_step": (hout.numel() + hgin.numel() + hgp.numel()) * 4,
+                "ms_per_step": sec * 1e3, "copy_floor_ms": floor * 1e3, "steps": k_e2e, "chunks": args.e2e_chunks,
+                "batches_in_flight": depth,
+                "api": "box_convolution.HostPipeline.submit/wait -> bc_boxconv2d_host_step (C ABI, pinned host buffers in and out, "
+                       "chunked copy/compute overlap on 3 streams; every batch's inputs go up and its results come back inside the "
+                       "timed region); copy_floor_ms = the same bytes as bare cudaMemcpyAsync in both directions at once, "
+                       "per rank, max over ranks"}
 
-    sampler.stop_flag = True
-    sampler.join(timeout=1.0)
-    clocks = sampler.summary(t_start, t_end)
-    if clocks["samples"] < 3:
-        wider = sampler.summary(t_start, t_busy_end)
-        wider["window"] = "timed region too short for NVML polling; includes the eager and end-to-end legs"
-        clocks = wider
+    def release(self):
+        self.graphs, self.outs, self.packed, self.xs, self.gos = None, [], [], [], []
+        torch.cuda.empty_cache()
+
+
+def training_config(name, world, strong):
+    """The keys of `config` that both arms print alike."""
+    full_n = CONFIGS[name][0]
+    per_gpu = full_n // world if strong else full_n
+    return {"workload": describe(name), "global_batch": per_gpu * world, "batch_per_gpu": per_gpu}
+
+
+def summarise_rounds(per_round, K, outputs_per_step):
+    med = statistics.median(per_round)
+    return {"ms_per_step": med / K, "value": outputs_per_step / (med / K * 1e-3) / 1e9,
+            "rounds": len(per_round), "round_ms_median": med, "round_ms_min": min(per_round),
+            "round_ms_max": max(per_round)}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    stage("process group ready (world %d)" % world)
+    # NVML is polled by rank 0 only, and only while a timed region is running
+    sampler = ClockSampler(local_rank, active=False) if rank == 0 else None
+    if sampler is not None:
+        sampler.start()
+
+    run = TrainingRun(args, args.workload, rank, world, dev)
+    wl = run.wl
+    N, C, F, h, w = wl.shape
+    stage("eager warm-up and graph capture")
+    run.warm_up_and_capture()
+    stage("timed region: rounds of %d steps" % args.steps)
+    per_round, (t_start, t_end) = run.timed_rounds(sampler)
+    main = summarise_rounds(per_round, args.steps, wl.outputs * world)
+    replay_only = run.replay_only_ms_per_step() if world > 1 else None
+    stage("eager repeat with per-kernel events")
+    roofline, eager_ms = run.per_kernel()
+
+    sharding = None
+    if world > 1:
+        stage("sharding check")
+        sharding = run.check_sharding()
+
+    e2e = None
+    if not args.skip_e2e:
+        stage("end-to-end leg")
+        e2e = run.end_to_end()
+
+    clocks = sampler.summary(t_start, t_end) if sampler is not None else None
 
     cpu_baseline = None
-    stage("cpu baseline")
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        stage("cpu baseline")
         ref = CpuReference()
         n = ref.pick_sample(args.workload, 6, 20.0)
         sample_wl = make_workload(args.workload, batch=n)
@@ -742,38 +935,77 @@ def run_ours(args, rank, world, local_rank):
                         "sample": "batch %d of %d of %s, 1 warm-up + 5 steps, mean %.3f s per step" % (
                             n, N, args.workload, sec)}
 
+    launches_per_step = run.launches_per_step
+    launch_text = ("eager" if run.graphs is None else
+                   "one cuda graph replay (clip+forward+backward) per step at every GPU count, %d buffer sets in turn%s" % (
+                       BUFFER_SETS, "; the step's all-reduce is issued asynchronously behind its replay and overlaps the next step"
+                       if world > 1 else ""))
+    run.release()
+
+    # the 1/8-frame block at batch 16 per GPU (BASELINE configuration 2) as an extra key of the same line
+    extra = None
+    if args.workload == "cfg5" and not args.skip_cfg2:
+        stage("cfg2 (batch 16 per GPU) for the extra key")
+        small = TrainingRun(args, "cfg2", rank, world, dev)
+        small.warm_up_and_capture()
+        rounds2, _ = small.timed_rounds(None)
+        extra = summarise_rounds(rounds2, args.steps, small.wl.outputs * world)
+        extra["roofline"], extra["eager_ms_per_step"] = small.per_kernel()
+        extra["hbm_gbs_step"] = small.wl.algorithmic_bytes * world / (extra["ms_per_step"] * 1e-3) / 1e9
+        extra["config"] = dict(training_config("cfg2", world, False), scaling="weak")
+        small.release()
+
+    if sampler is not None:
+        sampler.stop_flag = True
+        sampler.join(timeout=1.0)
+
+    failed = sharding is not None and sharding[0] != "ok"
     if rank == 0:
+        config = training_config(args.workload, world, run.strong)
+        config.update({
+            "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (BUFFER_SETS, wl.algorithmic_bytes / 1e6),
+            "launch": launch_text,
+            "rounds": main["rounds"], "round_ms_min": main["round_ms_min"], "round_ms_max": main["round_ms_max"],
+            "timing": "value = median over `rounds` consecutive rounds of `steps` steps, one CUDA event between rounds, "
+                      "max over ranks per round; barrier + synchronize before the first and after the last round",
+            "eager_ms_per_step": eager_ms,
+            "collective": "nccl all_reduce of the packed (4,C,F) parameter gradient" if world > 1 else "none"})
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": describe(args.workload), "global_batch": N * world, "batch_per_gpu": N,
-                       "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (
-                           BUFFER_SETS, wl.algorithmic_bytes / 1e6),
-                       "launch": "eager" if graphs is None else (
-                           "cuda graph replay of clip+forward+backward, %d consecutive steps (one per buffer set) per graph launch" % BUFFER_SETS
-                           if multi is not None else
-                           "cuda graph replay of clip+forward+backward, one graph per buffer set; all-reduce of step k on a side stream, overlapping step k+1"),
-                       "eager_ms_per_step": eager_ms,
-                       "collective": "nccl all_reduce of the packed (4,C,F) parameter gradient" if world > 1 else "none"},
-            "hbm_gbs_step": wl.algorithmic_bytes * world / (ms_per_step * 1e-3) / 1e9,
+            "metric": METRIC, "value": main["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": main["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong" if run.strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config,
+            "hbm_gbs_step": wl.algorithmic_bytes * world / (main["ms_per_step"] * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
+            "gpu_launches": int(launches_per_step * args.steps * main["rounds"]), "clocks": clocks,
         }
+        if replay_only is not None:
+            line["breakdown"] = {"replay_only_ms_per_step": replay_only, "with_allreduce_ms_per_step": main["ms_per_step"],
+                                 "note": "the same graph replays timed without and with the per-step all-reduce"}
+        if sharding is not None:
+            line["allreduce_check"] = sharding[0]
+            line["allreduce_check_max_rel_err"] = sharding[1]
+        if extra is not None:
+            line["cfg2"] = extra
         print(json.dumps(line), flush=True)
     stage("done")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("bench: the sharded results do not match the full batch: %r" % (sharding[1],))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="cfg2", choices=sorted(CONFIGS) + ["cfg4", "infer"])
+    ap.add_argument("--workload", default="cfg5", choices=sorted(CONFIGS) + ["cfg4", "infer"])
+    ap.add_argument("--rounds", type=int, default=0, help="timed rounds of --steps steps (0: at least 15, more until --min-timed-ms)")
+    ap.add_argument("--min-timed-ms", type=float, default=300.0, help="shortest timed region when --rounds is 0")
+    ap.add_argument("--skip-cfg2", action="store_true", help="cfg5 only: leave out the extra cfg2 key")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")

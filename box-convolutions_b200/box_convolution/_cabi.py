@@ -28,6 +28,7 @@ SIGNATURES = {
     "bc_box_convolution_backward_workspace": (_sz, [_i] * 6),
     "bc_box_convolution_backward": (_i, [_vp] * 7 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_clip_parameters": (_i, [_vp] * 4 + [_i, _d, _d, _d, _d, _i, _vp]),
+    "bc_clip_parameters_packed": (_i, [_vp] * 4 + [_i, _d, _d, _d, _d, _i, _vp, _vp]),
     "bc_integral_image_f64": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "bc_box_convolution_forward_f64": (_i, [_vp] * 6 + [_i] * 7 + [_vp]),
     "bc_box_convolution_backward_workspace_f64": (_sz, [_i] * 6),

@@ -182,3 +182,24 @@ def clip_parameters(x_min, x_max, y_min, y_max, reparametrization_h, reparametri
             *[p.data_ptr() for p in ps], x_min.numel(), float(reparametrization_h),
             float(reparametrization_w), float(max_input_h), float(max_input_w),
             int(bool(exact)), _stream()), "clip_parameters")
+
+
+def clip_parameters_packed(x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
+                           max_input_h, max_input_w, exact):
+    """``clip_parameters`` for contiguous float32 CUDA tensors that also returns a packed
+    ``(4,) + x_min.shape`` copy of the clipped values, written by the same launch.  The module
+    hands that copy to the autograd Function as the parameter snapshot of the step."""
+    ps = (x_min, x_max, y_min, y_max)
+    for p, n in zip(ps, ("x_min", "x_max", "y_min", "y_max")):
+        _require_cuda_float(p, n, torch.float32)
+        if not p.is_contiguous():
+            raise RuntimeError("%s must be contiguous" % n)
+    if not all(p.shape == x_min.shape for p in ps):
+        raise RuntimeError("box_convolution: parameter tensors differ in size")
+    packed = torch.empty((4,) + tuple(x_min.shape), dtype=torch.float32, device=x_min.device)
+    with torch.cuda.device(x_min.device):
+        check(lib.bc_clip_parameters_packed(
+            *[p.data_ptr() for p in ps], x_min.numel(), float(reparametrization_h),
+            float(reparametrization_w), float(max_input_h), float(max_input_w),
+            int(bool(exact)), packed.data_ptr(), _stream()), "clip_parameters")
+    return packed

@@ -38,21 +38,26 @@ def reparametrize(x_min, x_max, y_min, y_max, reparametrization_h, reparametriza
 
 class BoxConvolutionFunction(torch.autograd.Function):
     """apply(input, x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
-    normalize, exact) -> output (N, C*F, h, w).  The parameters are the stored ones."""
+    normalize, exact) -> output (N, C*F, h, w).  The parameters are the stored ones.
+
+    One optional tenth argument, used by the module: ``snapshot``, a packed float32 ``(4, C, F)``
+    copy of the four parameter tensors as they are at this call (``ext.clip_parameters_packed``
+    makes it while clipping).  Without it the Function copies the parameters itself."""
 
     @staticmethod
     def forward(ctx, input, x_min, x_max, y_min, y_max,
-                reparametrization_h, reparametrization_w, normalize, exact):
+                reparametrization_h, reparametrization_w, normalize, exact, snapshot=None):
         ctx.narrow = None
         if isinstance(input, torch.Tensor) and input.dtype in ext._NARROW:
             (input, x_min, x_max, y_min, y_max), ctx.narrow = ext._widen([input, x_min, x_max, y_min, y_max])
+            snapshot = None
         out = BoxConvolutionFunction._forward_wide(ctx, input, x_min, x_max, y_min, y_max, reparametrization_h,
-                                                   reparametrization_w, normalize, exact)
+                                                   reparametrization_w, normalize, exact, snapshot)
         return out if ctx.narrow is None else out.to(ctx.narrow)
 
     @staticmethod
     def _forward_wide(ctx, input, x_min, x_max, y_min, y_max,
-                      reparametrization_h, reparametrization_w, normalize, exact):
+                      reparametrization_h, reparametrization_w, normalize, exact, snapshot=None):
         _require_cuda_float(input, "input")
         if input.dim() != 4:
             raise RuntimeError("BoxConv2d: input must have 4 dimensions")
@@ -71,7 +76,17 @@ class BoxConvolutionFunction(torch.autograd.Function):
             raise RuntimeError("BoxConv2d: all parameters must have equal number of columns")
 
         input = input.contiguous()
-        params = [p.detach().contiguous() for p in params]
+        # The backward pass works on a snapshot of the parameters, as the reference saves fresh
+        # pixel-unit copies: the module changes its parameters in place (clipping) between a forward
+        # and the backward that belongs to it.  The module supplies the snapshot; otherwise one launch
+        # copies the four tensors into a packed buffer.  No snapshot when nothing will be differentiated.
+        if any(ctx.needs_input_grad[:5]):
+            if (snapshot is None or snapshot.dtype != input.dtype or snapshot.device != input.device
+                    or tuple(snapshot.shape) != (4, C, F) or not snapshot.is_contiguous()):
+                snapshot = torch.cat([p.detach().reshape(-1) for p in params]).view(4, C, F)
+            params = [snapshot[0], snapshot[1], snapshot[2], snapshot[3]]
+        else:
+            params = [p.detach().contiguous() for p in params]
         ctx.normalize, ctx.exact = bool(normalize), bool(exact)
         ctx.reparametrization_h, ctx.reparametrization_w = reparametrization_h, reparametrization_w
         ctx.chained = input.dtype == torch.float64
@@ -101,6 +116,11 @@ class BoxConvolutionFunction(torch.autograd.Function):
         return BoxConvolutionFunction._backward_wide(ctx, grad_output)
 
     @staticmethod
+    def _no_grads(ctx):
+        """None for every argument after the five differentiable ones."""
+        return (None,) * (len(ctx.needs_input_grad) - 5)
+
+    @staticmethod
     def _backward_wide(ctx, grad_output):
         if ctx.chained:
             input_integrated, x_min, x_max, y_min, y_max = ctx.saved_tensors
@@ -108,7 +128,7 @@ class BoxConvolutionFunction(torch.autograd.Function):
             grads = ext.box_convolution_backward(
                 input_integrated, x_min, x_max, y_min, y_max, grad_output, None,
                 ctx.reparametrization_h, ctx.reparametrization_w, ctx.normalize, ctx.exact, *needs)
-            return tuple(g if n else None for g, n in zip(grads, needs)) + (None,) * 4
+            return tuple(g if n else None for g, n in zip(grads, needs)) + BoxConvolutionFunction._no_grads(ctx)
         input, x_min, x_max, y_min, y_max = ctx.saved_tensors
         N, C, h, w = input.shape
         F = x_min.size(1)
@@ -134,4 +154,4 @@ class BoxConvolutionFunction(torch.autograd.Function):
                     grad_params.data_ptr() if grad_params is not None else None,
                     ws.data_ptr(), ws.numel(), _stream()), "BoxConv2d backward")
         grads = [grad_input] + [grad_params[i] if needs[1 + i] else None for i in range(4)]
-        return tuple(grads) + (None,) * 4
+        return tuple(grads) + BoxConvolutionFunction._no_grads(ctx)

@@ -85,11 +85,19 @@ class BoxConv2d(torch.nn.Module):
         return self
 
     def forward(self, input):
+        snapshot = None
         if self.training:
-            self._clip_parameters()
-        return BoxConvolutionFunction.apply(
-            input, self.x_min, self.x_max, self.y_min, self.y_max,
-            self.reparametrization_h, self.reparametrization_w, self.normalize, self.exact)
+            ps = self._parameters4()
+            if all(p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() for p in ps):
+                # the launch that clips also leaves the copy of the parameters that backward will use
+                snapshot = ext.clip_parameters_packed(
+                    *[p.data for p in ps], self.reparametrization_h, self.reparametrization_w,
+                    self.max_input_h, self.max_input_w, self.exact)
+            else:
+                self._clip_parameters()
+        args = (input, self.x_min, self.x_max, self.y_min, self.y_max,
+                self.reparametrization_h, self.reparametrization_w, self.normalize, self.exact)
+        return BoxConvolutionFunction.apply(*args) if snapshot is None else BoxConvolutionFunction.apply(*args, snapshot)
 
     def draw_boxes(self, channels=None, resolution=(600, 600), weights=None):
         """Rasterises the boxes into an ``(H, W, 3)`` uint8 numpy image for debugging: the frame

@@ -46,6 +46,9 @@ struct Fusion {
 
 // Records a CUDA launch error for bc_last_cuda_error() and maps it to a status code.
 int check_launch(const char *what);
+// For a runtime call that returned `e` != cudaSuccess: records it (whatever cudaGetLastError says:
+// cudaErrorNotReady, for one, is not sticky) and returns BC_ERR_CUDA.
+int cuda_failed(cudaError_t e, const char *what);
 
 // Kernel ids reported by the profiling aid (bc_profile_get / bc_kernel_name).
 enum KernelId {
@@ -59,7 +62,7 @@ struct LaunchScope {
     LaunchScope(int kernel_id, cudaStream_t stream);
     ~LaunchScope();
     cudaStream_t stream;
-    int slot;
+    cudaEvent_t after;      // null unless this launch is being timed
 };
 
 // ---- programmatic dependent launch ---------------------------------------------------------
@@ -113,7 +116,7 @@ int launch_backward_global(const T *x, const T *x_integ, const T *go_integ, cons
 
 template <typename T>
 int launch_clip(T *x_min, T *x_max, T *y_min, T *y_max, int count, double rep_h, double rep_w,
-                double max_h, double max_w, bool exact, cudaStream_t s);
+                double max_h, double max_w, bool exact, cudaStream_t s, T *packed = nullptr);
 
 template <typename T>
 int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int count, int per_box,

@@ -292,8 +292,8 @@ template <class K>
 int band_opt_in(K kernel, size_t bytes)
 {
     if (bytes <= 40 * 1024) return BC_OK;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
-        return check_launch("shared memory opt-in");
+    if (cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes))
+        return cuda_failed(e, "shared memory opt-in");
     return BC_OK;
 }
 

@@ -300,9 +300,10 @@ int launch_finish_param_grads(const T *partials, const BoxParamsT<T> &bp, int co
     const int blocks = (count + warps_per_block - 1) / warps_per_block;
     {
         LaunchScope scope(KID_FINISH_PARAM_GRADS, s);
-        if (launch_overlapped(finish_param_grads_kernel<T>, (unsigned)blocks, warps_per_block * 32, 0, s, partials, bp,
-                              count, per_box, normalize, exact, rep_h, rep_w, need_mask, grad_params) != cudaSuccess)
-            return check_launch("finish_param_grads");
+        if (cudaError_t e = launch_overlapped(finish_param_grads_kernel<T>, (unsigned)blocks, warps_per_block * 32, 0, s,
+                                              partials, bp, count, per_box, normalize, exact, rep_h, rep_w, need_mask,
+                                              grad_params))
+            return cuda_failed(e, "finish_param_grads");
     }
     return check_launch("finish_param_grads");
 }

@@ -632,8 +632,8 @@ template <class K>
 int opt_in_smem(K kernel, size_t bytes)
 {
     if (bytes <= 34 * 1024) return BC_OK;     // static scratch included, this stays under the 48 KB default
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
-        return check_launch("shared memory opt-in");
+    if (cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes))
+        return cuda_failed(e, "shared memory opt-in");
     return BC_OK;
 }
 
@@ -691,9 +691,9 @@ static int launch_forward_plane_impl(const float *x, const BoxParams &bp, const 
     const Fusion none{0, nullptr, nullptr, nullptr, 0};
     {
         LaunchScope scope(KID_FORWARD_PLANE, s);
-        if (launch_overlapped(kern, (unsigned)(planes * fsplit), warps * 32, smem, s, x, bp, out, C, F, h, w, fsplit,
-                              normalize, exact, fu ? *fu : none) != cudaSuccess)
-            return check_launch("forward_plane");
+        if (cudaError_t e = launch_overlapped(kern, (unsigned)(planes * fsplit), warps * 32, smem, s, x, bp, out, C, F, h, w,
+                                              fsplit, normalize, exact, fu ? *fu : none))
+            return cuda_failed(e, "forward_plane");
     }
     return check_launch("forward_plane");
 }
@@ -750,9 +750,9 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
     if (st != BC_OK) return st;
     {
         LaunchScope scope(KID_BACKWARD_PLANE, s);
-        if (launch_overlapped(kern, (unsigned)planes, warps * 32, smem, s, x, grad_output, bp, grad_input, partials, N,
-                              C, F, h, w, normalize, exact, write_gin) != cudaSuccess)
-            return check_launch("backward_plane");
+        if (cudaError_t e = launch_overlapped(kern, (unsigned)planes, warps * 32, smem, s, x, grad_output, bp, grad_input,
+                                              partials, N, C, F, h, w, normalize, exact, write_gin))
+            return cuda_failed(e, "backward_plane");
     }
     st = check_launch("backward_plane");
     if (st != BC_OK || !need_params) return st;
@@ -764,7 +764,7 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
 // (synchronises).  Nonzero means an asynchronous copy never signalled completion.
 int read_wait_timeouts(int *count)
 {
-    if (cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(int)) != cudaSuccess) return check_launch("read_wait_timeouts");
+    if (cudaError_t e = cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(int))) return cuda_failed(e, "read_wait_timeouts");
     return BC_OK;
 }
 

@@ -20,28 +20,42 @@ int check_launch(const char *what)
     return BC_ERR_CUDA;
 }
 
+int cuda_failed(cudaError_t e, const char *what)
+{
+    cudaGetLastError();     // clear the sticky copy, if the error left one
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    return BC_ERR_CUDA;
+}
+
 // ---- launch counter and per-kernel event timing
 static std::atomic<uint64_t> g_launches{0};
 static std::mutex g_prof_mutex;
-static bool g_prof_on = false;
+static std::atomic<bool> g_prof_on{false};
 static int g_prof_used = 0;
 struct ProfRecord { int kid; cudaEvent_t a, b; };
 static std::vector<ProfRecord> g_prof;
 
-LaunchScope::LaunchScope(int kernel_id, cudaStream_t s) : stream(s), slot(-1)
+LaunchScope::LaunchScope(int kernel_id, cudaStream_t s) : stream(s), after(nullptr)
 {
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (!g_prof_on) return;
-    std::lock_guard<std::mutex> lock(g_prof_mutex);
-    if (!g_prof_on || g_prof_used >= (int)g_prof.size()) return;
-    slot = g_prof_used++;
-    g_prof[slot].kid = kernel_id;
-    cudaEventRecord(g_prof[slot].a, stream);
+    if (!g_prof_on.load(std::memory_order_acquire)) return;
+    cudaEvent_t before;
+    {
+        // the record table may be grown by bc_profile_start() on another thread: take the two
+        // events out under the lock and never touch the table again from this scope
+        std::lock_guard<std::mutex> lock(g_prof_mutex);
+        if (!g_prof_on.load(std::memory_order_relaxed) || g_prof_used >= (int)g_prof.size()) return;
+        ProfRecord &r = g_prof[g_prof_used++];
+        r.kid = kernel_id;
+        before = r.a;
+        after = r.b;
+    }
+    cudaEventRecord(before, stream);
 }
 
 LaunchScope::~LaunchScope()
 {
-    if (slot >= 0) cudaEventRecord(g_prof[slot].b, stream);
+    if (after) cudaEventRecord(after, stream);
 }
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -116,8 +130,8 @@ static int backward_entry(const T *input_integrated, const T *x_min, const T *x_
             if (!grad_params) return BC_ERR_NULL_POINTER;
             for (int j = 0; j < 4; ++j)
                 if (need_mask & (BC_NEED_X_MIN << j))
-                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(T) * C * F, stream) != cudaSuccess)
-                        return check_launch("memset");
+                    if (cudaError_t e = cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(T) * C * F, stream))
+                        return cuda_failed(e, "memset");
         }
         return BC_OK;
     }
@@ -142,14 +156,14 @@ static int backward_entry(const T *input_integrated, const T *x_min, const T *x_
 template <typename T>
 static int clip_entry(T *x_min, T *x_max, T *y_min, T *y_max, int count, double reparametrization_h,
                       double reparametrization_w, double max_input_h, double max_input_w, int exact,
-                      cudaStream_t stream)
+                      cudaStream_t stream, T *packed = nullptr)
 {
     if (count < 0) return BC_ERR_BAD_SHAPE;
     if (count == 0) return BC_OK;
     if (!x_min || !x_max || !y_min || !y_max) return BC_ERR_NULL_POINTER;
     if (reparametrization_h == 0.0 || reparametrization_w == 0.0) return BC_ERR_BAD_SHAPE;
     return launch_clip<T>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
-                          max_input_h, max_input_w, exact != 0, stream);
+                          max_input_h, max_input_w, exact != 0, stream, packed);
 }
 
 }  // namespace bc
@@ -249,6 +263,16 @@ int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, i
 {
     return clip_entry<float>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
                              max_input_h, max_input_w, exact, stream);
+}
+
+int bc_clip_parameters_packed(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+                              double reparametrization_h, double reparametrization_w,
+                              double max_input_h, double max_input_w, int exact, float *packed_out,
+                              bc_stream_t stream)
+{
+    if (count > 0 && !packed_out) return BC_ERR_NULL_POINTER;
+    return clip_entry<float>(x_min, x_max, y_min, y_max, count, reparametrization_h, reparametrization_w,
+                             max_input_h, max_input_w, exact, stream, packed_out);
 }
 
 int bc_clip_parameters_f64(double *x_min, double *x_max, double *y_min, double *y_max, int count,
@@ -352,8 +376,8 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
             if (!grad_params) return BC_ERR_NULL_POINTER;
             for (int j = 0; j < 4; ++j)
                 if (need_mask & (BC_NEED_X_MIN << j))
-                    if (cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream) != cudaSuccess)
-                        return check_launch("memset");
+                    if (cudaError_t e = cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream))
+                        return cuda_failed(e, "memset");
         }
         return BC_OK;
     }
@@ -397,17 +421,20 @@ static void *static_scratch_address(int *status)
     static std::mutex mutex;
     static void *address[64] = {nullptr};
     int device = -1;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
-        *status = check_launch("bc_boxconv2d_backward_static: cudaGetDevice");
-        if (*status == BC_OK) *status = BC_ERR_UNSUPPORTED;
+    if (cudaError_t e = cudaGetDevice(&device)) {
+        *status = cuda_failed(e, "bc_boxconv2d_backward_static: cudaGetDevice");
+        return nullptr;
+    }
+    if (device < 0 || device >= 64) {
+        *status = BC_ERR_UNSUPPORTED;
         return nullptr;
     }
     std::lock_guard<std::mutex> lock(mutex);
     if (!address[device]) {
         void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) {
-            *status = check_launch("bc_boxconv2d_backward_static: cudaGetSymbolAddress");
-            if (*status == BC_OK) *status = BC_ERR_CUDA;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            *status = cuda_failed(e, "bc_boxconv2d_backward_static: cudaGetSymbolAddress");
             return nullptr;
         }
         address[device] = p;
@@ -452,19 +479,20 @@ int bc_profile_start(int capacity)
     std::lock_guard<std::mutex> lock(g_prof_mutex);
     while ((int)g_prof.size() < capacity) {
         ProfRecord r{0, nullptr, nullptr};
-        if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess)
-            return check_launch("bc_profile_start");
+        cudaError_t e = cudaEventCreate(&r.a);
+        if (e == cudaSuccess) e = cudaEventCreate(&r.b);
+        if (e != cudaSuccess) return cuda_failed(e, "bc_profile_start");
         g_prof.push_back(r);
     }
     g_prof_used = 0;
-    g_prof_on = true;
+    g_prof_on.store(true, std::memory_order_release);
     return BC_OK;
 }
 
 int bc_profile_stop(void)
 {
     std::lock_guard<std::mutex> lock(g_prof_mutex);
-    g_prof_on = false;
+    g_prof_on.store(false, std::memory_order_release);
     return BC_OK;
 }
 
@@ -479,8 +507,9 @@ int bc_profile_get(int index, int *kernel_id, float *milliseconds)
     std::lock_guard<std::mutex> lock(g_prof_mutex);
     if (index < 0 || index >= g_prof_used || !kernel_id || !milliseconds) return BC_ERR_BAD_SHAPE;
     *kernel_id = g_prof[index].kid;
-    if (cudaEventElapsedTime(milliseconds, g_prof[index].a, g_prof[index].b) != cudaSuccess)
-        return check_launch("bc_profile_get");
+    // (cudaErrorNotReady until the device has passed both events: synchronise first)
+    if (cudaError_t e = cudaEventElapsedTime(milliseconds, g_prof[index].a, g_prof[index].b))
+        return cuda_failed(e, "bc_profile_get");
     return BC_OK;
 }
 

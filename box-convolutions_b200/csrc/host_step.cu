@@ -50,17 +50,33 @@ __global__ void sum_chunk_grads_kernel(const float *__restrict__ chunks, int n_c
     out[i] = s;
 }
 
-// Events used to order the three streams; host-side objects, created on first use per thread.
-cudaEvent_t *events(int n)
+// Events used to order the three streams; host-side objects, created on first use per thread and
+// per device (an event belongs to the device that was current when it was created, and the three
+// streams of a call are streams of the current device).
+constexpr int kMaxDevices = 64;
+cudaEvent_t *events(int n, cudaError_t *err)
 {
-    static thread_local std::vector<cudaEvent_t> pool;
+    static thread_local std::vector<cudaEvent_t> pools[kMaxDevices];
+    int device = -1;
+    *err = cudaGetDevice(&device);
+    if (*err != cudaSuccess) return nullptr;
+    if (device < 0 || device >= kMaxDevices) { *err = cudaErrorInvalidDevice; return nullptr; }
+    std::vector<cudaEvent_t> &pool = pools[device];
     while ((int)pool.size() < n) {
         cudaEvent_t e;
-        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        *err = cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+        if (*err != cudaSuccess) return nullptr;
         pool.push_back(e);
     }
     return pool.data();
 }
+
+// First error of a chain of runtime calls, so that a failure is reported with its own code.
+struct Chain {
+    cudaError_t e = cudaSuccess;
+    Chain &operator()(cudaError_t r) { if (e == cudaSuccess) e = r; return *this; }
+    bool failed() const { return e != cudaSuccess; }
+};
 
 }  // namespace
 
@@ -99,8 +115,9 @@ int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, f
     float *gp_chunks = reinterpret_cast<float *>(ws + L.gp_chunks), *gp_sum = reinterpret_cast<float *>(ws + L.gp_sum);
     void *scratch = ws + L.scratch;
 
-    cudaEvent_t *ev = events(2 * chunks + 1);
-    if (!ev) return check_launch("bc_boxconv2d_host_step: event pool");
+    cudaError_t ev_err = cudaSuccess;
+    cudaEvent_t *ev = events(2 * chunks + 1, &ev_err);
+    if (!ev) return cuda_failed(ev_err, "bc_boxconv2d_host_step: event pool");
 
     int st = BC_OK;
     if (clip) {
@@ -116,11 +133,12 @@ int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, f
         const size_t xo = (size_t)n0 * C * plane, oo = xo * F;
         const size_t xb = (size_t)nk * C * plane * sizeof(float), ob = xb * F;
         // inputs of chunk k
-        if (cudaMemcpyAsync(x_dev + xo, x_host + xo, xb, cudaMemcpyHostToDevice, copy_in) != cudaSuccess ||
-            cudaMemcpyAsync(go_dev + oo, grad_output_host + oo, ob, cudaMemcpyHostToDevice, copy_in) != cudaSuccess ||
-            cudaEventRecord(ev[2 * k], copy_in) != cudaSuccess ||
-            cudaStreamWaitEvent(compute, ev[2 * k], 0) != cudaSuccess)
-            return check_launch("bc_boxconv2d_host_step: input copies");
+        Chain in;
+        in(cudaMemcpyAsync(x_dev + xo, x_host + xo, xb, cudaMemcpyHostToDevice, copy_in));
+        if (!in.failed()) in(cudaMemcpyAsync(go_dev + oo, grad_output_host + oo, ob, cudaMemcpyHostToDevice, copy_in));
+        if (!in.failed()) in(cudaEventRecord(ev[2 * k], copy_in));
+        if (!in.failed()) in(cudaStreamWaitEvent(compute, ev[2 * k], 0));
+        if (in.failed()) return cuda_failed(in.e, "bc_boxconv2d_host_step: input copies");
         // kernels of chunk k (they share the scratch area: same stream, so in order)
         st = bc_boxconv2d_forward(x_dev + xo, x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w,
                                   out_dev + oo, nk, C, F, h, w, normalize, exact, scratch, L.scratch_bytes, compute);
@@ -130,11 +148,12 @@ int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, f
                                    gin_dev + xo, gp_chunks + (size_t)k * 4 * C * F, scratch, L.scratch_bytes, compute);
         if (st != BC_OK) return st;
         // results of chunk k
-        if (cudaEventRecord(ev[2 * k + 1], compute) != cudaSuccess ||
-            cudaStreamWaitEvent(copy_out, ev[2 * k + 1], 0) != cudaSuccess ||
-            cudaMemcpyAsync(out_host + oo, out_dev + oo, ob, cudaMemcpyDeviceToHost, copy_out) != cudaSuccess ||
-            cudaMemcpyAsync(grad_input_host + xo, gin_dev + xo, xb, cudaMemcpyDeviceToHost, copy_out) != cudaSuccess)
-            return check_launch("bc_boxconv2d_host_step: result copies");
+        Chain res;
+        res(cudaEventRecord(ev[2 * k + 1], compute));
+        if (!res.failed()) res(cudaStreamWaitEvent(copy_out, ev[2 * k + 1], 0));
+        if (!res.failed()) res(cudaMemcpyAsync(out_host + oo, out_dev + oo, ob, cudaMemcpyDeviceToHost, copy_out));
+        if (!res.failed()) res(cudaMemcpyAsync(grad_input_host + xo, gin_dev + xo, xb, cudaMemcpyDeviceToHost, copy_out));
+        if (res.failed()) return cuda_failed(res.e, "bc_boxconv2d_host_step: result copies");
     }
     {
         const int count = 4 * C * F;
@@ -143,10 +162,12 @@ int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, f
     }
     st = check_launch("sum_chunk_grads");
     if (st != BC_OK) return st;
-    if (cudaEventRecord(ev[2 * chunks], compute) != cudaSuccess ||
-        cudaStreamWaitEvent(copy_out, ev[2 * chunks], 0) != cudaSuccess ||
-        cudaMemcpyAsync(grad_params_host, gp_sum, (size_t)4 * C * F * sizeof(float), cudaMemcpyDeviceToHost, copy_out) != cudaSuccess)
-        return check_launch("bc_boxconv2d_host_step: gradient copy");
+    Chain fin;
+    fin(cudaEventRecord(ev[2 * chunks], compute));
+    if (!fin.failed()) fin(cudaStreamWaitEvent(copy_out, ev[2 * chunks], 0));
+    if (!fin.failed())
+        fin(cudaMemcpyAsync(grad_params_host, gp_sum, (size_t)4 * C * F * sizeof(float), cudaMemcpyDeviceToHost, copy_out));
+    if (fin.failed()) return cuda_failed(fin.e, "bc_boxconv2d_host_step: gradient copy");
     return BC_OK;
 }
 

@@ -387,9 +387,9 @@ int launch_integral_image<double>(const double *in, double *out, int64_t planes,
     const size_t smem = ((size_t)tile_rows * pw + (size_t)w) * sizeof(double);
     if (smem > 200 * 1024) return BC_ERR_UNSUPPORTED;
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(integral_image_f64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return check_launch("integral_image (f64): shared memory opt-in");
+        if (cudaError_t e = cudaFuncSetAttribute(integral_image_f64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem))
+        return cuda_failed(e, "integral_image (f64): shared memory opt-in");
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);
@@ -445,8 +445,8 @@ int launch_integral_image_f32(const float *in, float *out, int64_t planes, int h
                    : (pipelined ? integral_image_kernel<true, true>
                                 : (vec4 ? integral_image_kernel<true, false> : integral_image_kernel<false, false>));
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return check_launch("integral_image: shared memory opt-in");
+        if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem))
+        return cuda_failed(e, "integral_image: shared memory opt-in");
     }
     {
         LaunchScope scope(KID_INTEGRAL, s);

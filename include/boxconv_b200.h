@@ -99,6 +99,16 @@ int bc_clip_parameters(float *x_min, float *x_max, float *y_min, float *y_max, i
                        double reparametrization_h, double reparametrization_w,
                        double max_input_h, double max_input_w, int exact, bc_stream_t stream);
 
+/* The same projection, which in addition leaves a packed (4, count) copy of the clipped values
+ * (x_min, x_max, y_min, y_max) in packed_out: the snapshot of its parameters that a training
+ * forward pass keeps for the backward pass (the reference's autograd Function makes fresh
+ * pixel-unit copies, box_convolution/box_convolution_function.py:36-42,51), taken by the launch
+ * that clips instead of by a copy kernel of its own. */
+int bc_clip_parameters_packed(float *x_min, float *x_max, float *y_min, float *y_max, int count,
+                              double reparametrization_h, double reparametrization_w,
+                              double max_input_h, double max_input_w, int exact, float *packed_out,
+                              bc_stream_t stream);
+
 /* ---- float64 forms of the four functions above ----------------------------------------
  * The reference dispatches its operator over floating types (AT_DISPATCH_FLOATING_TYPES_AND_HALF,
  * src/box_convolution_interface.cpp:51,201; src/integral_image_interface.cpp:8-27) and its own

@@ -18,6 +18,7 @@ Output: ``oracle/_ref/box_convolution_cpp_cuda.so`` (git-ignored; it travels wit
 tree to machines that have the same torch build but no reference checkout).
 
 Usage:  python oracle/build_ref.py [--reference /path/to/box-convolutions]
+(default: $BOXCONV_REFERENCE, else a folder `reference` beside this repository)
 """
 import argparse
 import os
@@ -36,14 +37,24 @@ SOURCES = [
 ]
 
 
+def reference_root():
+    """Where the reference checkout is: the BOXCONV_REFERENCE environment variable, else a folder
+    `reference` beside this repository; None when neither exists."""
+    for cand in (os.environ.get("BOXCONV_REFERENCE"),
+                 os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src")):
+            return cand
+    return None
+
+
 def built_path():
     return os.path.join(OUT_DIR, EXT_NAME + ".so")
 
 
 def build(reference_root, verbose=False):
     """Compile the extension if the reference checkout is present.  Returns the .so path or None."""
-    src_dir = os.path.join(reference_root, "src")
-    if not os.path.isdir(src_dir):
+    src_dir = os.path.join(reference_root or "", "src")
+    if not reference_root or not os.path.isdir(src_dir):
         return built_path() if os.path.exists(built_path()) else None
     if os.path.exists(built_path()):
         newest_src = max(os.path.getmtime(os.path.join(src_dir, f)) for f in SOURCES)
@@ -88,7 +99,8 @@ def load_ref():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("BOXCONV_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=reference_root(),
+                    help="reference checkout (default: $BOXCONV_REFERENCE, else ../reference beside the repository)")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
     p = build(a.reference, a.verbose)

@@ -7,9 +7,15 @@ The reference's compiled module (built from its sources by ``oracle/build_ref.py
 outputs are stored together in ``boxconv_golden.npz`` so the fixtures can be checked on machines
 that have neither the reference checkout nor its build.
 
-Run from the repository root, on a machine that has the reference checkout:
+The initial box draw of the reference's ``BoxConv2d`` module (Python's ``random``, its
+``reset_parameters``) is stored as well, for two seeded constructions of the reference's own class.
+
+Run from the repository root, on a machine that has the reference checkout (its path in
+BOXCONV_REFERENCE, or a folder ``reference`` beside the repository):
     python oracle/build_ref.py && python tests/golden/make_golden.py
 """
+import importlib.util
+import random
 import os
 import sys
 
@@ -47,6 +53,22 @@ def draw_boxes(rng, C, F, h, w, far_outside=False, integer_coords=False):
             return ps
         if all((np.abs(p - np.round(p)) > 0.012).all() for p in ps):
             return ps
+
+
+def reference_package(ref_ext):
+    """The reference's Python package, imported under another name (ours is called the same), with
+    its compiled module name bound to the CPU build."""
+    root = build_ref.reference_root()
+    if root is None:
+        raise SystemExit("no reference checkout: set BOXCONV_REFERENCE")
+    sys.modules["box_convolution_cpp_cuda"] = ref_ext
+    pkg_dir = os.path.join(root, "box_convolution")
+    spec = importlib.util.spec_from_file_location("reference_box_convolution", os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["reference_box_convolution"] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def main():
@@ -117,6 +139,17 @@ def main():
         blob[pre + "rep"] = np.array([rep_h, rep_w], np.float64)
         blob[pre + "before"] = before
         blob[pre + "after"] = np.stack([t.numpy() for t in tp])
+
+    # ---- the module's initial draw (box_convolution/box_convolution_module.py:69-97), stored values
+    pkg = reference_package(ref)
+    reset_cases = [(2, 3, 64, 128, 8.0, 123), (4, 4, 32, 32, 0.86, 7)]
+    blob["reset_count"] = np.int64(len(reset_cases))
+    for i, (C, F, mh, mw, factor, seed) in enumerate(reset_cases):
+        random.seed(seed)
+        m = pkg.BoxConv2d(C, F, mh, mw, reparametrization_factor=factor)
+        blob["reset%d_meta" % i] = np.array([C, F, mh, mw, seed], np.int64)
+        blob["reset%d_factor" % i] = np.float64(factor)
+        blob["reset%d_params" % i] = np.stack([p.detach().numpy() for p in (m.x_min, m.x_max, m.y_min, m.y_max)])
 
     np.savez_compressed(OUT, **blob)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(blob), "arrays")

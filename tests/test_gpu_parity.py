@@ -115,6 +115,42 @@ def test_clip_golden_bitwise(bc, golden):
         assert np.array_equal(got, golden[pre + "after"]), i
 
 
+def test_clip_packed_equals_clip_plus_copy(bc, golden):
+    from box_convolution import ext
+    for i in range(int(golden["clip_count"])):
+        pre = "clip%d_" % i
+        C, F, mh, mw, exact = [int(v) for v in golden[pre + "meta"]]
+        rep_h, rep_w = [float(v) for v in golden[pre + "rep"]]
+        ps = [cuda(p) for p in golden[pre + "before"]]
+        packed = ext.clip_parameters_packed(*ps, rep_h, rep_w, mh, mw, bool(exact))
+        assert packed.shape == (4, C, F)
+        assert np.array_equal(packed.cpu().numpy(), golden[pre + "after"]), i
+        assert np.array_equal(np.stack([p.cpu().numpy() for p in ps]), golden[pre + "after"]), i
+
+
+def test_backward_uses_the_parameters_of_its_own_forward(bc):
+    """The reference saves copies of the parameters at forward time.  Changing the module's parameters
+    between forward and backward (a second forward that clips, an optimizer step, eval()) must not
+    change the gradients of the first forward."""
+    wl = make_workload("cfg1", batch=2, planes=4)
+    want = run_module(bc, wl.x, wl.stored, wl.grad_output, wl.max_h, wl.max_w, 8, True, True)
+    for train in (True, False):
+        C, F = wl.stored[0].shape
+        m = bc.BoxConv2d(C, F, wl.max_h, wl.max_w, reparametrization_factor=8).cuda()
+        with torch.no_grad():
+            for p, v in zip((m.x_min, m.x_max, m.y_min, m.y_max), wl.stored):
+                p.copy_(cuda(v))
+        m.train(train)
+        xt = cuda(wl.x).requires_grad_()
+        out = m(xt)
+        for p in (m.x_min, m.x_max, m.y_min, m.y_max):
+            p.data.mul_(0.5)                                # no version bump, like the module's own clip
+        out.backward(cuda(wl.grad_output))
+        assert np.array_equal(xt.grad.cpu().numpy(), want[1])
+        for p, g in zip((m.x_min, m.x_max, m.y_min, m.y_max), want[2]):
+            assert np.array_equal(p.grad.cpu().numpy(), g)
+
+
 # ------------------------------------------------------------------ module / autograd Function
 def run_module(bc, x, stored, go, max_h, max_w, factor, normalize, exact, train=True):
     C, F = stored[0].shape

@@ -25,25 +25,18 @@ def test_fields_and_state_dict_layout():
         bc.BoxConv2d(1, 1, 8, 8, stride_h=2)
 
 
-def test_reset_parameters_follows_the_reference_draw():
-    """Same use of Python's `random` as box_convolution/box_convolution_module.py:69-97: centre_h,
-    centre_w, height, width per box, all stretched by 1.5, then divided by the reparametrization."""
+def test_reset_parameters_follows_the_reference_draw(golden):
+    """The stored parameters of a freshly constructed module equal, bit for bit, those of the
+    reference's own BoxConv2d built under the same `random.seed` (fixtures written by
+    tests/golden/make_golden.py from box_convolution/box_convolution_module.py:69-97)."""
+    for i in range(int(golden["reset_count"])):
+        C, F, mh, mw, seed = [int(v) for v in golden["reset%d_meta" % i]]
+        random.seed(seed)
+        m = bc.BoxConv2d(C, F, mh, mw, reparametrization_factor=float(golden["reset%d_factor" % i]))
+        got = np.stack([p.detach().numpy() for p in (m.x_min, m.x_max, m.y_min, m.y_max)])
+        assert np.array_equal(got, golden["reset%d_params" % i]), i
     random.seed(123)
-    m = bc.BoxConv2d(2, 3, 64, 128)
-    random.seed(123)
-    exp = [[], [], [], []]
-    for _ in range(6):
-        rh, rw = 64 * 2 / 4.8 - 1, 128 * 2 / 4.8 - 1
-        ch = random.uniform(-rh + 1, rh - 1)
-        cw = random.uniform(-rw + 1, rw - 1)
-        hh = 2 * random.uniform(1, min(rh - ch, ch + rh))
-        ww = 2 * random.uniform(1, min(rw - cw, cw + rw))
-        for lst, v in zip(exp, (ch - hh / 2, ch + hh / 2, cw - ww / 2, cw + ww / 2)):
-            lst.append(v * 1.5)
-    for p, vals, rep in zip((m.x_min, m.x_max, m.y_min, m.y_max), exp, (512, 512, 1024, 1024)):
-        want = torch.tensor(vals, dtype=torch.float32).view(2, 3) * (1 / rep)
-        assert torch.equal(p.detach(), want)
-    pix = m.get_actual_parameters()
+    pix = bc.BoxConv2d(2, 3, 64, 128).get_actual_parameters()
     assert all((b - a >= 2.99).all() for a, b in ((pix[0], pix[1]), (pix[2], pix[3])))   # min size 2 * 1.5
 
 
