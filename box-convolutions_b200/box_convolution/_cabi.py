@@ -40,6 +40,9 @@ SIGNATURES = {
     "bc_boxconv2d_backward_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_backward": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_boxconv2d_backward_static": (_i, [_vp] * 6 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp]),
+    "bc_boxconv2d_narrow_supported": (_i, [_i] * 3),
+    "bc_boxconv2d_forward_narrow": (_i, [_vp, _i] + [_vp] * 4 + [_f, _f, _vp] + [_i] * 7 + [_vp]),
+    "bc_boxconv2d_backward_narrow": (_i, [_vp, _i] + [_vp] * 5 + [_f, _f] + [_i] * 8 + [_vp, _vp, _vp, _sz, _vp]),
     "bc_boxconv2d_host_step_workspace": (_sz, [_i] * 6),
     "bc_boxconv2d_host_step": (_i, [_vp] * 9 + [_f, _f, _d, _d] + [_i] * 9 + [_vp, _sz, _vp, _vp, _vp]),
     "bc_launch_count": (ctypes.c_uint64, []),
@@ -56,6 +59,7 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn.restype = _res
     _fn.argtypes = _args
 
+BC_IO_F16, BC_IO_BF16 = 1, 2
 BC_NEED_INPUT, BC_NEED_X_MIN, BC_NEED_X_MAX, BC_NEED_Y_MIN, BC_NEED_Y_MAX = 1, 2, 4, 8, 16
 
 

@@ -8,9 +8,10 @@ takes from the saved output is recomputed, so only the input and the four parame
 kept alive between forward and backward.
 
 float64 tensors (gradient checks) take the general kernels through the four extension functions,
-chained as the reference chains them.  float16 / bfloat16 tensors are storage only: the Function
-widens them to float32 on the device, runs the float32 kernels and rounds results and gradients
-back.
+chained as the reference chains them.  float16 / bfloat16 tensors: planes that the shared-memory
+kernels hold are read and written in their 16-bit type by those kernels (float arithmetic on chip,
+float parameter gradients rounded at the end); for larger planes the Function makes float copies,
+runs the float kernels and rounds results and gradients back.
 """
 import torch
 
@@ -48,12 +49,83 @@ class BoxConvolutionFunction(torch.autograd.Function):
     def forward(ctx, input, x_min, x_max, y_min, y_max,
                 reparametrization_h, reparametrization_w, normalize, exact, snapshot=None):
         ctx.narrow = None
+        ctx.narrow_kernels = False
         if isinstance(input, torch.Tensor) and input.dtype in ext._NARROW:
+            out = BoxConvolutionFunction._forward_narrow(ctx, input, x_min, x_max, y_min, y_max, reparametrization_h,
+                                                         reparametrization_w, normalize, exact)
+            if out is not None:
+                return out
+            # planes that the shared-memory kernels do not hold: float copies, float kernels
             (input, x_min, x_max, y_min, y_max), ctx.narrow = ext._widen([input, x_min, x_max, y_min, y_max])
             snapshot = None
         out = BoxConvolutionFunction._forward_wide(ctx, input, x_min, x_max, y_min, y_max, reparametrization_h,
                                                    reparametrization_w, normalize, exact, snapshot)
         return out if ctx.narrow is None else out.to(ctx.narrow)
+
+    @staticmethod
+    def _forward_narrow(ctx, input, x_min, x_max, y_min, y_max,
+                        reparametrization_h, reparametrization_w, normalize, exact):
+        """float16 / bfloat16 tensors on the kernels that read and write them as they are (the
+        reference's half instantiations, src/box_convolution_cuda_forward.cu:224).  Returns None when
+        the shape is not served that way."""
+        params = (x_min, x_max, y_min, y_max)
+        if not (input.is_cuda and input.dim() == 4 and all(isinstance(p, torch.Tensor) and p.is_cuda and p.dim() == 2
+                                                           and p.device == input.device for p in params)):
+            return None
+        N, C, h, w = input.shape
+        F = x_min.size(1)
+        if not all(tuple(p.shape) == (C, F) and p.dtype == input.dtype for p in params):
+            return None
+        if not lib.bc_boxconv2d_narrow_supported(F, h, w):
+            return None
+        input = input.contiguous()
+        # the parameters (and later their gradients) are small: float copies of them
+        wide = torch.cat([p.detach().reshape(-1) for p in params]).float().view(4, C, F)
+        kind = _cabi.BC_IO_F16 if input.dtype == torch.float16 else _cabi.BC_IO_BF16
+        out = torch.empty((N, C * F, h, w), dtype=input.dtype, device=input.device)
+        with torch.cuda.device(input.device):
+            check(lib.bc_boxconv2d_forward_narrow(
+                input.data_ptr(), kind, *[wide[i].data_ptr() for i in range(4)],
+                float(reparametrization_h), float(reparametrization_w), out.data_ptr(),
+                N, C, F, h, w, int(bool(normalize)), int(bool(exact)), _stream()), "BoxConv2d forward")
+        ctx.normalize, ctx.exact = bool(normalize), bool(exact)
+        ctx.reparametrization_h, ctx.reparametrization_w = reparametrization_h, reparametrization_w
+        ctx.chained = False
+        ctx.narrow_kernels = True
+        ctx.io_kind = kind
+        ctx.save_for_backward(input, wide)
+        return out
+
+    @staticmethod
+    def _backward_narrow(ctx, grad_output):
+        input, wide = ctx.saved_tensors
+        N, C, h, w = input.shape
+        F = wide.size(2)
+        needs = ctx.needs_input_grad[:5]
+        mask = sum(1 << i for i, b in enumerate(needs) if b)
+        grad_input = grad_params = None
+        if mask:
+            if grad_output.dtype != input.dtype:
+                grad_output = grad_output.to(input.dtype)
+            grad_output = grad_output.contiguous()
+            dev = input.device
+            if needs[0]:
+                grad_input = torch.empty_like(input)
+            if any(needs[1:]):
+                grad_params = torch.empty((4, C, F), dtype=torch.float32, device=dev)
+            with torch.cuda.device(dev):
+                ws = _workspace(lib.bc_boxconv2d_backward_workspace(N, C, F, h, w, mask), dev)
+                check(lib.bc_boxconv2d_backward_narrow(
+                    input.data_ptr(), ctx.io_kind, *[wide[i].data_ptr() for i in range(4)], grad_output.data_ptr(),
+                    float(ctx.reparametrization_h), float(ctx.reparametrization_w),
+                    N, C, F, h, w, int(ctx.normalize), int(ctx.exact), mask,
+                    grad_input.data_ptr() if grad_input is not None else None,
+                    grad_params.data_ptr() if grad_params is not None else None,
+                    ws.data_ptr(), ws.numel(), _stream()), "BoxConv2d backward")
+            if grad_params is not None:
+                grad_params = grad_params.to(input.dtype)
+        grads = [grad_input] + [grad_params[i] if needs[1 + i] else None for i in range(4)]
+        return tuple(grads) + BoxConvolutionFunction._no_grads(ctx)
 
     @staticmethod
     def _forward_wide(ctx, input, x_min, x_max, y_min, y_max,
@@ -110,6 +182,8 @@ class BoxConvolutionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
+        if ctx.narrow_kernels:
+            return BoxConvolutionFunction._backward_narrow(ctx, grad_output)
         if ctx.narrow is not None:
             grads = BoxConvolutionFunction._backward_wide(ctx, grad_output.float())
             return tuple(g.to(ctx.narrow) if g is not None else None for g in grads)

@@ -17,7 +17,7 @@ OUT = os.path.join(HERE, "box_convolution", "libboxconv_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
+    "-O3", "-lineinfo", "-std=c++17", "--threads", "0", "-Xcompiler", "-fPIC", "-shared",
 ]
 
 

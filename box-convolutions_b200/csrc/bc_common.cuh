@@ -145,6 +145,15 @@ int launch_backward_plane(const float *x, const float *grad_output, const BoxPar
                           cudaStream_t s);
 
 int read_wait_timeouts(int *count);
+int read_wait_timeouts_narrow(int *count);
+
+// The same whole-plane kernels on float16 / bfloat16 tensors (box_plane_half.cu); io_kind is
+// BC_IO_F16 or BC_IO_BF16, the parameters, partial sums and parameter gradients are float.
+int launch_forward_plane_narrow(const void *x, int io_kind, const BoxParams &bp, void *out, int N, int C, int F, int h,
+                                int w, bool normalize, bool exact, cudaStream_t s);
+int launch_backward_plane_narrow(const void *x, const void *grad_output, int io_kind, const BoxParams &bp, float rep_h,
+                                 float rep_w, int N, int C, int F, int h, int w, bool normalize, bool exact,
+                                 int need_mask, void *grad_input, float *grad_params, float *partials, cudaStream_t s);
 
 // Column-band kernels for planes that do not fit in shared memory whole (box_band_smem.cu): they
 // gather from integral images in global memory in the padded row layout

@@ -411,6 +411,61 @@ int bc_boxconv2d_backward(const float *input, const float *x_min, const float *x
                                   need_mask, grad_input, grad_params, partials, stream);
 }
 
+// ---- float16 / bfloat16 tensors on the shared-memory kernels
+int bc_boxconv2d_narrow_supported(int F, int h, int w)
+{
+    return (F > 0 && h > 0 && w > 0 && plane_path_fits_forward(F, h, w) && plane_path_fits_backward(F, h, w)) ? 1 : 0;
+}
+
+int bc_boxconv2d_forward_narrow(const void *input, int io_kind, const float *x_min, const float *x_max,
+                                const float *y_min, const float *y_max, float reparametrization_h,
+                                float reparametrization_w, void *output, int N, int C, int F, int h,
+                                int w, int normalize, int exact, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (io_kind != BC_IO_F16 && io_kind != BC_IO_BF16) return BC_ERR_UNSUPPORTED;
+    if (any_empty(N, C, F, h, w)) return BC_OK;
+    if (!input || !x_min || !x_max || !y_min || !y_max || !output) return BC_ERR_NULL_POINTER;
+    if (!plane_path_fits_forward(F, h, w)) return BC_ERR_UNSUPPORTED;
+    const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
+    return launch_forward_plane_narrow(input, io_kind, bp, output, N, C, F, h, w, normalize != 0, exact != 0, stream);
+}
+
+int bc_boxconv2d_backward_narrow(const void *input, int io_kind, const float *x_min, const float *x_max,
+                                 const float *y_min, const float *y_max, const void *grad_output,
+                                 float reparametrization_h, float reparametrization_w, int N, int C,
+                                 int F, int h, int w, int normalize, int exact, int need_mask,
+                                 void *grad_input, float *grad_params, void *workspace,
+                                 size_t workspace_bytes, bc_stream_t stream)
+{
+    if (!sizes_ok(N, C, F, h, w)) return BC_ERR_BAD_SHAPE;
+    if (io_kind != BC_IO_F16 && io_kind != BC_IO_BF16) return BC_ERR_UNSUPPORTED;
+    need_mask &= BC_NEED_ALL;
+    if (!need_mask) return BC_OK;
+    const bool need_params = (need_mask & ~BC_NEED_INPUT) != 0;
+    if (any_empty(N, C, F, h, w)) {
+        if (need_params && C > 0 && F > 0) {
+            if (!grad_params) return BC_ERR_NULL_POINTER;
+            for (int j = 0; j < 4; ++j)
+                if (need_mask & (BC_NEED_X_MIN << j))
+                    if (cudaError_t e = cudaMemsetAsync(grad_params + (size_t)j * C * F, 0, sizeof(float) * C * F, stream))
+                        return cuda_failed(e, "memset");
+        }
+        return BC_OK;
+    }
+    if (!input || !x_min || !x_max || !y_min || !y_max || !grad_output) return BC_ERR_NULL_POINTER;
+    if ((need_mask & BC_NEED_INPUT) && !grad_input) return BC_ERR_NULL_POINTER;
+    if (need_params && !grad_params) return BC_ERR_NULL_POINTER;
+    if (!plane_path_fits_backward(F, h, w)) return BC_ERR_UNSUPPORTED;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+        workspace_bytes < bc_boxconv2d_backward_workspace(N, C, F, h, w, need_mask))
+        return BC_ERR_WORKSPACE;
+    const BoxParams bp{x_min, x_max, y_min, y_max, reparametrization_h, reparametrization_w};
+    return launch_backward_plane_narrow(input, grad_output, io_kind, bp, reparametrization_h, reparametrization_w, N, C,
+                                        F, h, w, normalize != 0, exact != 0, need_mask, grad_input, grad_params,
+                                        static_cast<float *>(workspace), stream);
+}
+
 // ---- backward pass on the library's own scratch array (see the header for who needs this)
 static __device__ __align__(256) unsigned char g_static_scratch[BC_STATIC_SCRATCH_BYTES];
 

@@ -190,6 +190,31 @@ int bc_boxconv2d_host_step(const float *x_host, const float *grad_output_host, f
                            void *workspace, size_t workspace_bytes, bc_stream_t copy_in,
                            bc_stream_t compute, bc_stream_t copy_out);
 
+/* ---- float16 / bfloat16 tensors ---------------------------------------------------------
+ * The reference instantiates every kernel of the operator for at::Half
+ * (AT_DISPATCH_FLOATING_TYPES_AND_HALF: src/box_convolution_cuda_forward.cu:224,
+ * src/box_convolution_cuda_backward.cu:176,431, src/integral_image_cuda.cu:79).  These are
+ * bc_boxconv2d_forward() / bc_boxconv2d_backward() for tensors stored in a 16-bit type: input,
+ * grad_output, output and grad_input are arrays of 16-bit values of kind io_kind, read and written
+ * as they are (no widened copies in global memory); the box parameters, the scratch memory and
+ * grad_params are float, and so are the integral images and all arithmetic on chip (a 16-bit
+ * integral image, which the reference's dispatch produces, loses the low bits of every box sum).
+ * Served for planes that the shared-memory kernels hold: bc_boxconv2d_narrow_supported() tells;
+ * other shapes return BC_ERR_UNSUPPORTED and the caller converts to float.  Scratch size as for the
+ * float functions. */
+enum { BC_IO_F16 = 1, BC_IO_BF16 = 2 };
+int bc_boxconv2d_narrow_supported(int F, int h, int w);
+int bc_boxconv2d_forward_narrow(const void *input, int io_kind, const float *x_min, const float *x_max,
+                                const float *y_min, const float *y_max, float reparametrization_h,
+                                float reparametrization_w, void *output, int N, int C, int F, int h,
+                                int w, int normalize, int exact, bc_stream_t stream);
+int bc_boxconv2d_backward_narrow(const void *input, int io_kind, const float *x_min, const float *x_max,
+                                 const float *y_min, const float *y_max, const void *grad_output,
+                                 float reparametrization_h, float reparametrization_w, int N, int C,
+                                 int F, int h, int w, int normalize, int exact, int need_mask,
+                                 void *grad_input, float *grad_params, void *workspace,
+                                 size_t workspace_bytes, bc_stream_t stream);
+
 /* ---- backward pass without caller-supplied scratch memory --------------------------------
  * This entry point has no counterpart in the reference (which allocates its temporaries with
  * at::empty on every call).  It is bc_boxconv2d_backward() for hosts that have no way to hand

@@ -53,6 +53,51 @@ def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row():
                 assert max_rel(gp[k], gp_ref[k]) < 1e-3, (cfg, repeat, k)
 
 
+def test_static_scratch_backward_takes_no_device_memory_and_serves_need_mask_subsets():
+    """The property the entry point exists for: device memory in use is the same before and after the
+    calls (the first call on the device included), and gradient subsets behave as with a workspace."""
+    from box_convolution import _cabi
+    lib = _cabi.lib
+    wl = make_workload("cfg1", batch=2, planes=3)
+    x = torch.from_numpy(wl.x).cuda()
+    go = torch.from_numpy(wl.grad_output).cuda()
+    stored = [torch.from_numpy(p).cuda() for p in wl.stored]
+    N, C, h, w = x.shape
+    F = stored[0].shape[1]
+    masks = (31, 1, 30, 10)
+    refs = {mask: _backward(lib, False, x, go, stored, wl.rep_h, wl.rep_w, mask) for mask in masks}
+    outs = {mask: (torch.full_like(x, float("nan")), torch.full((4, C, F), float("nan"), device="cuda")) for mask in masks}
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    # nothing between the two readings but the calls themselves (no tensor operations, which could
+    # make PyTorch's own allocator ask the driver for memory)
+    free_before, _ = torch.cuda.mem_get_info()
+    allocated_before = torch.cuda.memory_allocated()
+    statuses = {}
+    for mask in masks:
+        gin, gp = outs[mask]
+        statuses[mask] = lib.bc_boxconv2d_backward_static(
+            x.data_ptr(), *[p.data_ptr() for p in stored], go.data_ptr(), wl.rep_h, wl.rep_w,
+            N, C, F, h, w, 1, 1, mask, gin.data_ptr(), gp.data_ptr(), stream)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_allocated() == allocated_before
+    assert free_after == free_before
+    for mask in masks:
+        assert statuses[mask] == 0, (mask, lib.bc_status_string(statuses[mask]))
+        gin, gp = (t.cpu().numpy() for t in outs[mask])
+        _, gin_ref, gp_ref = refs[mask]
+        if mask & 1:
+            assert max_rel(gin, gin_ref) < 1e-4, mask
+        else:
+            assert np.isnan(gin).all(), mask                    # not asked for: untouched
+        for k in range(4):
+            if mask & (2 << k):
+                assert max_rel(gp[k], gp_ref[k]) < 1e-3, (mask, k)
+            else:
+                assert np.isnan(gp[k]).all(), (mask, k)
+
+
 def test_static_scratch_backward_refuses_what_does_not_fit():
     from box_convolution import _cabi
     lib = _cabi.lib
