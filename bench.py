@@ -77,11 +77,13 @@ BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds t
 # DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
 # profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
 NCU_TRAFFIC = {
-    # ncu capture of the plane kernels on cfg2 (summary under profiles/): 83.93 MB read + 4.00 MB written on cfg2 (4 194 304 input
-    # elements); below the 100.7 MB algorithmic figure because the 126 MB L2 still holds part of the
-    # 16.8 MB grad_input when the kernel ends
-    "backward_plane_kernel": (87.93e6, 4194304),
-    "forward_plane_kernel": (25.81e6, 4194304),
+    # ncu capture of the plane kernels on cfg2 (profiles/plane_kernels_cfg2_ncu_full.md): 83.93 MB read + 4.32 MB
+    # written by the backward kernel on cfg2 (4 194 304 input elements); below the 100.7 MB algorithmic figure
+    # because the 126 MB L2 still holds most of the 16.8 MB grad_input when the kernel ends.  Forward: 16.82 MB
+    # read + 12.24 MB written (most of its 67 MB output is still in L2 at kernel end).  Traffic grows in
+    # proportion to the planes processed, so a launch's figure is scaled by its input elements.
+    "backward_plane_kernel": (88.25e6, 4194304),
+    "forward_plane_kernel": (29.05e6, 4194304),
 }
 
 
@@ -160,7 +162,7 @@ def run_reference(args, rank, world):
     value = wl.outputs / sec / 1e9
     sample = "batch %d of %d of %s per step, %d steps, mean" % (n, CONFIGS[args.workload][0], args.workload, args.steps)
     strong = args.workload == "cfg5"
-    config = training_config(args.workload, args.gpus, strong)
+    config = training_config(args.workload, args.gpus, strong, args.shard_of)
     config.update({
         "l2": "host memory: no device buffers",
         "launch": "host loop over the reference's four extension functions, as its autograd Function calls them",
@@ -536,7 +538,10 @@ class TrainingRun:
         if self.strong and full_n % world:
             raise SystemExit("cfg5: the global batch of %d does not divide over %d GPUs" % (full_n, world))
         # the host copy of the workload feeds buffer set 0 of rank 0, the end-to-end leg and the CPU baseline
-        self.wl = wl = make_workload(name, batch=full_n // world if self.strong else None)
+        shards = world * max(1, getattr(args, "shard_of", 1) // world) if self.strong else 1
+        if self.strong and full_n % shards:
+            raise SystemExit("cfg5: the global batch of %d does not divide into %d shards" % (full_n, shards))
+        self.wl = wl = make_workload(name, batch=full_n // shards if self.strong else None)
         N, C, F, h, w = wl.shape
         self.module = m = bc.BoxConv2d(C, F, wl.max_h, wl.max_w, reparametrization_factor=8, normalize=True).to(dev)
         with torch.no_grad():
@@ -870,10 +875,10 @@ class TrainingRun:
         torch.cuda.empty_cache()
 
 
-def training_config(name, world, strong):
+def training_config(name, world, strong, shard_of=1):
     """The keys of `config` that both arms print alike."""
     full_n = CONFIGS[name][0]
-    per_gpu = full_n // world if strong else full_n
+    per_gpu = full_n // (world * max(1, shard_of // world)) if strong else full_n
     return {"workload": describe(name), "global_batch": per_gpu * world, "batch_per_gpu": per_gpu}
 
 
@@ -961,7 +966,7 @@ def run_ours(args, rank, world, local_rank):
 
     failed = sharding is not None and sharding[0] != "ok"
     if rank == 0:
-        config = training_config(args.workload, world, run.strong)
+        config = training_config(args.workload, world, run.strong, args.shard_of)
         config.update({
             "l2": "rotating %d input/output buffer sets (%.0f MB touched per set)" % (BUFFER_SETS, wl.algorithmic_bytes / 1e6),
             "launch": launch_text,
@@ -1006,6 +1011,9 @@ def main():
     ap.add_argument("--rounds", type=int, default=0, help="timed rounds of --steps steps (0: at least 15, more until --min-timed-ms)")
     ap.add_argument("--min-timed-ms", type=float, default=300.0, help="shortest timed region when --rounds is 0")
     ap.add_argument("--skip-cfg2", action="store_true", help="cfg5 only: leave out the extra cfg2 key")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="cfg5 only: give every rank the shard it would have in a job of this many GPUs (e.g. "
+                         "`--gpus 1 --shard-of 8` times one GPU's share of the 8-GPU job, without the collective)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")

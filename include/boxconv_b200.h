@@ -230,7 +230,10 @@ int bc_boxconv2d_backward_narrow(const void *input, int io_kind, const float *x_
  *    20 bytes per (sample, plane, filter), so the array covers N*C*F up to about 200 000; larger
  *    planes need a full set of integral images and fit only when tiny.
  *  - The first call on each device looks up the array's device address (with that device
- *    current); make that first call outside any stream capture.  No call allocates or frees.
+ *    current); make that first call outside any stream capture.  A call with N = 0 and
+ *    need_mask = BC_NEED_INPUT launches nothing and needs no valid pointers, but does that look-up:
+ *    the cheap way to make the first call.  No call allocates or frees.  The address is kept for
+ *    the life of the process: after cudaDeviceReset() this entry point must not be used any more.
  *  - All calls on a device share the one array and it keeps what the previous call left.  Nothing
  *    in it has to start at zero: every word a call reads was written earlier by that same call.
  *    Two calls that overlap on the GPU (different streams, or graphs replayed concurrently) race

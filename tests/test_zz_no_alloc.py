@@ -98,6 +98,16 @@ def test_static_scratch_backward_takes_no_device_memory_and_serves_need_mask_sub
                 assert np.isnan(gp[k]).all(), (mask, k)
 
 
+def test_static_scratch_backward_empty_call_is_the_cheap_first_call():
+    from box_convolution import _cabi
+    lib = _cabi.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    # N = 0, grad-input only: nothing to launch, no pointer is looked at, only the address look-up happens
+    st = lib.bc_boxconv2d_backward_static(None, None, None, None, None, None, 8.0, 8.0,
+                                          0, 4, 4, 64, 128, 1, 1, 1, None, None, stream)
+    assert st == 0
+
+
 def test_static_scratch_backward_refuses_what_does_not_fit():
     from box_convolution import _cabi
     lib = _cabi.lib
