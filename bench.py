@@ -168,14 +168,14 @@ def run_reference(args, rank, world):
         "launch": "host loop over the reference's four extension functions, as its autograd Function calls them",
         "rounds": 1, "round_ms_min": sec * 1e3 * args.steps, "round_ms_max": sec * 1e3 * args.steps,
         "timing": "mean host wall time of `steps` steps on a bounded sample of the batch (see cpu_baseline.sample)",
-        "eager_ms_per_step": sec * 1e3, "collective": "none",
-        "host_threads": ref.cores, "os_cpu_count": os.cpu_count()})
+        "eager_ms_per_step": sec * 1e3, "collective": "none"})
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config,
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": sample,
+                         "os_cpu_count": os.cpu_count()},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
