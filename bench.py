@@ -947,7 +947,7 @@ def run_ours(args, rank, world, local_rank):
                        if world > 1 else ""))
     run.release()
 
-    # the 1/8-frame block at batch 16 per GPU (BASELINE configuration 2) as an extra key of the same line
+    # the 1/8-frame block at batch 16 per GPU (the cfg2 workload) as an extra key of the same line
     extra = None
     if args.workload == "cfg5" and not args.skip_cfg2:
         stage("cfg2 (batch 16 per GPU) for the extra key")

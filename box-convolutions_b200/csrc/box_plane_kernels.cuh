@@ -27,8 +27,14 @@
 // stored with the layout above (conflict-free).
 //
 // The kernels are instantiated twice: FAST for planes whose height is a multiple of 8 and width
-// a multiple of 4 with 16-byte aligned tensors (no per-row guards, 128-bit global accesses), and
+// a multiple of 4 with aligned tensors (no per-row guards, one vector access per strip row), and
 // a guarded version for everything else.
+//
+// This file holds the kernels and their launchers as templates over the storage type of the big
+// tensors (Io<> below); box_plane_smem.cu instantiates them for float, box_plane_half.cu for
+// __half and __nv_bfloat16.  What limits these kernels is the shared-memory data pipe: every
+// output value takes about five 4-byte words from the integral image in shared memory, against
+// four bytes of HBM traffic.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
