@@ -92,7 +92,8 @@ def test_cityscapes_models_run_on_this_package(source, cls, n_boxes):
         a = model(frame)
         b = model(frame)
     # (cuDNN may pick non-deterministic convolution algorithms: close, not necessarily bit-equal)
-    assert torch.isfinite(a).all() and torch.allclose(a, b, rtol=1e-4, atol=1e-5)
+    assert torch.isfinite(a).all() and torch.isfinite(b).all()
+    assert float((a - b).abs().max()) <= 1e-3 * float(a.abs().max())
     assert all(not m.exact and not m.training for m in box_modules(model))
 
 
