@@ -74,17 +74,28 @@ def arm_watchdog(seconds):
 METRIC = "BoxConv2d fwd+bwd output Gelem/s"
 UNIT = "Gelem/s"
 BUFFER_SETS = 4          # rotated between steps so that the footprint exceeds the 126 MB L2
-# DRAM bytes (read+write) per launch of the dominant kernel from the ncu capture summarised in
-# profiles/, keyed by kernel name -> (bytes, units it was captured on); scaled by units at run time.
+# DRAM bytes (read+write) per launch of the plane kernels from the ncu captures summarised in profiles/,
+# keyed by kernel name -> [(bytes, input elements of the captured launch), ...].  A run takes the capture
+# whose size is closest to its own launches and scales it by the input elements (traffic grows in
+# proportion to the planes processed; how much of the output is still in the 126 MB L2 when the kernel
+# ends differs between a 16-sample and a 256-sample launch, hence two captures).
 NCU_TRAFFIC = {
-    # ncu capture of the plane kernels on cfg2 (profiles/plane_kernels_cfg2_ncu_full.md): 83.93 MB read + 4.32 MB
-    # written by the backward kernel on cfg2 (4 194 304 input elements); below the 100.7 MB algorithmic figure
-    # because the 126 MB L2 still holds most of the 16.8 MB grad_input when the kernel ends.  Forward: 16.82 MB
-    # read + 12.24 MB written (most of its 67 MB output is still in L2 at kernel end).  Traffic grows in
-    # proportion to the planes processed, so a launch's figure is scaled by its input elements.
-    "backward_plane_kernel": (88.25e6, 4194304),
-    "forward_plane_kernel": (29.05e6, 4194304),
+    # profiles/plane_kernels_cfg2_ncu_full.md (batch 16: 4 194 304 input elements) and
+    # profiles/plane_kernels_cfg5_dram_bytes.md (batch 256: 67 108 864 input elements)
+    "backward_plane_kernel": [(88.25e6, 4194304), (1591.1e6, 67108864)],
+    "forward_plane_kernel": [(29.05e6, 4194304), (1281.5e6, 67108864)],
 }
+
+
+def ncu_traffic(kernel, elements):
+    """(bytes, text) for a launch over `elements` input elements, or (None, None)."""
+    caps = NCU_TRAFFIC.get(kernel)
+    if not caps or elements <= 0:
+        return None, None
+    b, units = min(caps, key=lambda c: abs(np.log(c[1] / elements)))
+    text = ("ncu capture of this kernel on a launch of %d input elements (summary under profiles/)%s; "
+            "a constant, not measured by this run" % (units, "" if units == elements else ", scaled by the elements per launch"))
+    return b * elements / units, text
 
 
 def describe(name):
@@ -729,14 +740,9 @@ class TrainingRun:
             peak, peak_src = measured_peak()
             if alg is not None:
                 achieved = alg / (kernels[top]["mean_us"] * 1e-6) / 1e9
-                traffic = None
-                if top in NCU_TRAFFIC:
-                    b, units = NCU_TRAFFIC[top]
-                    traffic = b * (N * C * h * w) / units
+                traffic, traffic_source = ncu_traffic(top, N * C * h * w)
                 roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                            "frac": achieved / peak, "traffic": traffic,
-                            "traffic_source": None if traffic is None else
-                            "ncu capture of an earlier run of this kernel (summary under profiles/), scaled by the elements per launch; a constant, not measured by this run",
+                            "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
                             "algorithmic_bytes": alg, "mean_us": kernels[top]["mean_us"], "peak_source": peak_src,
                             "kernels": {k: round(v["mean_us"], 2) for k, v in kernels.items()}}
         return roofline, eager_ms
