@@ -232,7 +232,9 @@ int bc_boxconv2d_backward_narrow(const void *input, int io_kind, const float *x_
  *  - The first call on each device looks up the array's device address (with that device
  *    current); make that first call outside any stream capture.  A call with N = 0 and
  *    need_mask = BC_NEED_INPUT launches nothing and needs no valid pointers, but does that look-up:
- *    the cheap way to make the first call.  No call allocates or frees.  The address is kept for
+ *    the cheap way to make the first call.  No call allocates or frees; with the CUDA driver's lazy
+ *    module loading the first call is also when the array itself is placed on the device (device
+ *    memory in use grows by its size once, then stays).  The address is kept for
  *    the life of the process: after cudaDeviceReset() this entry point must not be used any more.
  *  - All calls on a device share the one array and it keeps what the previous call left.  Nothing
  *    in it has to start at zero: every word a call reads was written earlier by that same call.

