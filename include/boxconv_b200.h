@@ -251,8 +251,9 @@ int bc_boxconv2d_backward_static(const float *input, const float *x_min, const f
  * bc_launch_count(): kernels launched by this library since it was loaded.
  * bc_profile_*: while enabled, every kernel launch is bracketed by a pair of CUDA events on the
  * launching stream, so that a benchmark can read per-kernel device times of a normal run.
- * Events are host-side objects created by bc_profile_start(); recording must not be enabled
- * while a stream is being captured into a CUDA graph.  After a device synchronisation,
+ * Events are host-side objects created by bc_profile_start() on the device that is current at that
+ * call, so one process profiles one device (launches on streams of another device fail to record);
+ * recording must not be enabled while a stream is being captured into a CUDA graph.  After a device synchronisation,
  * bc_profile_get(i, ...) returns kernel id and milliseconds of record i;
  * bc_kernel_name(id) names the kernel. */
 uint64_t bc_launch_count(void);
