@@ -126,6 +126,11 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
     asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
 }
+// Hint that `bytes` (a multiple of 16) at `src` (16-byte aligned) will be copied soon: brings them into L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity)
 {
     const long long t0 = clock64();
@@ -547,6 +552,7 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
         __syncthreads();                                   // barriers initialised before anyone waits
         if (tid == 0) {
             bulk_load(sG32, gbase, plane_bytes, mbarG);
+            if (F > 1) bulk_prefetch_l2(gbase + (int64_t)npix, plane_bytes);
             if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
         }
     }
@@ -579,6 +585,8 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
                 // every thread has taken its block out of the staging buffer (barrier above)
                 fence_proxy_async();
                 bulk_load(sG32, gbase + (f + 1) * (int64_t)npix, plane_bytes, mbarG);
+                // the plane after that one on its way to L2 already (about 1 % on 256-sample batches)
+                if (f + 2 < F) bulk_prefetch_l2(gbase + (f + 2) * (int64_t)npix, plane_bytes);
             }
             build_columns<T, FAST>(blk, st, sRow, sCol, g, cg, rg);
         }
