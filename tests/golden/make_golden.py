@@ -55,6 +55,21 @@ def draw_boxes(rng, C, F, h, w, far_outside=False, integer_coords=False):
             return ps
 
 
+def border_boxes(h, w, exact):
+    """(x_min, x_max, y_min, y_max) in pixels: edges with fractional part 0 or 1/2, boxes ending on
+    the plane's border or one pixel beyond it, the smallest box, the largest the clip allows."""
+    return [
+        (-2.0, 3.0, -4.0, 1.0),
+        (-1.5, 2.5, 0.5, 6.5),
+        (0.0, 0.0, 0.0, 0.0) if exact else (0.0, 1.0, 0.0, 1.0),
+        (-(h - 1.0), 0.0, -(w - 1.0), 0.0),
+        (0.0, h - 1.0, 0.0, w - 1.0),
+        (-float(h), h - 2.0, -float(w), w - 2.0),
+        (-(h + 1.0), h - 1.0, -(w + 1.0), w - 1.0),
+        (3.0, 7.25, -9.75, -2.0),
+    ]
+
+
 def reference_package(ref_ext):
     """The reference's Python package, imported under another name (ours is called the same), with
     its compiled module name bound to the CPU build."""
@@ -150,6 +165,35 @@ def main():
         blob["reset%d_meta" % i] = np.array([C, F, mh, mw, seed], np.int64)
         blob["reset%d_factor" % i] = np.float64(factor)
         blob["reset%d_params" % i] = np.stack([p.detach().numpy() for p in (m.x_min, m.x_max, m.y_min, m.y_max)])
+
+    # ---- boxes on integer and half-integer coordinates and on the plane's borders, every mode; own
+    # random stream, so that the arrays above do not depend on this block
+    erng = np.random.default_rng(777)
+    edge_cases = [(1, 2, 8, 12, 20, n, e) for n in (True, False) for e in (True, False)]
+    blob["edge_count"] = np.int64(len(edge_cases))
+    for i, (N, C, F, h, w, normalize, exact) in enumerate(edge_cases):
+        x = erng.standard_normal((N, C, h, w)).astype(np.float32)
+        go = erng.standard_normal((N, C * F, h, w)).astype(np.float32)
+        boxes = border_boxes(h, w, exact)
+        params = [np.empty((C, F), np.float32) for _ in range(4)]
+        for c in range(C):
+            for f in range(F):
+                for k in range(4):
+                    params[k][c, f] = boxes[(f + c) % len(boxes)][k]
+        tp = [torch.from_numpy(p) for p in params]
+        integ = ref.integral_image(torch.from_numpy(x))
+        out = ref.box_convolution_forward(integ, *tp, normalize, exact)
+        res = ref.box_convolution_backward(
+            integ, *tp, torch.from_numpy(go), out if normalize else torch.empty(0),
+            1.0, 1.0, normalize, exact, True, True, True, True, True)
+        pre = "edge%d_" % i
+        blob[pre + "meta"] = np.array([N, C, F, h, w, int(normalize), int(exact)], np.int64)
+        blob[pre + "x"] = x
+        blob[pre + "go"] = go
+        blob[pre + "params"] = np.stack(params)
+        blob[pre + "out"] = out.numpy()
+        blob[pre + "gin"] = res[0].numpy()
+        blob[pre + "gparams"] = np.stack([r.numpy() for r in res[1:]])
 
     np.savez_compressed(OUT, **blob)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(blob), "arrays")

@@ -184,6 +184,24 @@ def test_function_golden(bc, golden):
             assert max_rel(params[k].grad.cpu().numpy() * np.float32(rep), golden[pre + "gparams"][k]) < 2e-4, (i, k)
 
 
+def test_function_golden_border_and_integer_boxes(bc, golden):
+    """The reference's own results for boxes on integer and half-integer coordinates and on the
+    plane's borders (fixtures `edge*`, all four modes)."""
+    assert int(golden["edge_count"]) == 4
+    for i in range(int(golden["edge_count"])):
+        pre = "edge%d_" % i
+        N, C, F, h, w, normalize, exact = [int(v) for v in golden[pre + "meta"]]
+        params = [cuda(p).requires_grad_() for p in golden[pre + "params"]]
+        x = cuda(golden[pre + "x"]).requires_grad_()
+        out = bc.BoxConvolutionFunction.apply(x, *params, 1.0, 1.0, bool(normalize), bool(exact))
+        out.backward(cuda(golden[pre + "go"]))
+        assert out.shape == (N, C * F, h, w)
+        assert max_rel(out.detach().cpu().numpy(), golden[pre + "out"].reshape(N, C * F, h, w)) < 1e-5, i
+        assert max_rel(x.grad.cpu().numpy(), golden[pre + "gin"]) < 1e-5, i
+        for k in range(4):
+            assert max_rel(params[k].grad.cpu().numpy(), golden[pre + "gparams"][k]) < 2e-4, (i, k)
+
+
 @pytest.mark.parametrize("cfg", ["cfg1", "cfg2"])
 def test_module_full_config_vs_oracle(bc, cfg):
     wl = make_workload(cfg)
@@ -245,6 +263,45 @@ def test_module_random_shapes_vs_oracle(bc, shape, normalize, exact):
         assert max_rel(params[k].grad.cpu().numpy(), ref[1 + k]) < TOL_PARAM, k
     if outside:
         assert (out.detach().view(N, C, F, h, w)[:, 0, 0] == 0).all()
+
+
+@pytest.mark.parametrize("normalize,exact", [(True, True), (False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("shape", [(2, 2, 8, 64, 128), (1, 1, 8, 40, 131), (1, 1, 8, 203, 301)])
+def test_boxes_on_integer_coordinates_and_plane_borders_vs_oracle(bc, shape, normalize, exact):
+    """Box edges whose fractional part is exactly zero or one half, boxes that end exactly on the
+    plane's border or one pixel beyond it, one-pixel boxes, and a box as large as the clip allows:
+    the cases in which ceil/floor of an edge coincide with the edge (`src/box_convolution.cpp:14-40`)
+    and in which tap rows and columns are clamped on one side only."""
+    N, C, F, h, w = shape
+    rng = np.random.default_rng(h + w + 3 * int(normalize) + 5 * int(exact))
+    x = rng.standard_normal((N, C, h, w)).astype(np.float32)
+    go = rng.standard_normal((N, C * F, h, w)).astype(np.float32)
+    boxes = [                                    # (x_min, x_max, y_min, y_max) in pixels
+        (-2.0, 3.0, -4.0, 1.0),                  # integers
+        (-1.5, 2.5, 0.5, 6.5),                   # half-integers
+        (0.0, 0.0, 0.0, 0.0) if exact else (0.0, 1.0, 0.0, 1.0),     # the smallest box
+        (-(h - 1.0), 0.0, -(w - 1.0), 0.0),      # reaches exactly the first row / column from the last pixel
+        (0.0, h - 1.0, 0.0, w - 1.0),            # reaches exactly the last row / column from the first pixel
+        (-float(h), h - 2.0, -float(w), w - 2.0),    # one pixel beyond the border on the low side
+        (-(h + 1.0), h - 1.0, -(w + 1.0), w - 1.0),  # the clip's limits
+        (3.0, 7.25, -9.75, -2.0),                # integer on one side, fraction on the other
+    ]
+    pix = [np.empty((C, F), np.float32) for _ in range(4)]
+    for c in range(C):
+        for f in range(F):
+            for k in range(4):
+                pix[k][c, f] = boxes[(f + c) % len(boxes)][k]
+    params = [cuda(p).requires_grad_() for p in pix]
+    xt = cuda(x).requires_grad_()
+    out = bc.BoxConvolutionFunction.apply(xt, *params, 1.0, 1.0, normalize, exact)
+    out.backward(cuda(go))
+    integ = oracle.integral_image(x)
+    ref_out = oracle.box_convolution_forward(integ, *pix, normalize, exact)
+    ref = oracle.box_convolution_backward(integ, *pix, go, ref_out, 1.0, 1.0, normalize, exact)
+    assert max_rel(out.detach().cpu().numpy(), ref_out) < TOL_OUT
+    assert max_rel(xt.grad.cpu().numpy(), ref[0]) < TOL_GIN
+    for k in range(4):
+        assert max_rel(params[k].grad.cpu().numpy(), ref[1 + k]) < TOL_PARAM, k
 
 
 def test_module_empty_batch_and_strided_inputs(bc):

@@ -36,6 +36,23 @@ def test_backward_matches_reference(golden):
             assert max_rel(res[1 + k], golden[pre + "gparams"][k]) < 2e-5, (i, k)
 
 
+def test_border_and_integer_boxes_match_reference(golden):
+    """Boxes on integer and half-integer coordinates, on the plane's borders and at the clip's limits,
+    in all four modes: outputs bit for bit, gradients up to the order of summation."""
+    assert int(golden["edge_count"]) == 4
+    for i in range(int(golden["edge_count"])):
+        pre = "edge%d_" % i
+        N, C, F, h, w, normalize, exact = golden[pre + "meta"]
+        integ = oracle.integral_image(golden[pre + "x"])
+        out = oracle.box_convolution_forward(integ, *golden[pre + "params"], normalize, exact)
+        assert np.array_equal(out.reshape(-1), golden[pre + "out"].reshape(-1)), i
+        res = oracle.box_convolution_backward(integ, *golden[pre + "params"], golden[pre + "go"],
+                                              golden[pre + "out"], 1.0, 1.0, normalize, exact)
+        assert max_rel(res[0], golden[pre + "gin"]) < 2e-6, i
+        for k in range(4):
+            assert max_rel(res[1 + k], golden[pre + "gparams"][k]) < 2e-5, (i, k)
+
+
 def test_backward_respects_need_mask(golden):
     pre = "bc2_"
     N, C, F, h, w, normalize, exact, _ = golden[pre + "meta"]
