@@ -534,7 +534,10 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
 #pragma unroll
     for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
 
-    if (STAGED && tid == 0) {
+    // The first copies are started by a thread of the second warp (when there is one), so that they do
+    // not queue behind the box arithmetic of the first warp's threads.
+    const int starter = blockDim.x > 32 ? 32 : 0;
+    if (STAGED && tid == starter) {
         mbar_init(mbarX, 1);
         mbar_init(mbarG, 1);
         fence_mbar_init();
@@ -544,18 +547,17 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
     // registers and shared memory only up to here; now global memory that the kernel in front of
     // this one in the stream may still be using
     grid_dependency_wait();
+    if (STAGED && tid == starter) {
+        // (the thread that initialised the barriers: it needs no barrier to use them)
+        bulk_load(sG32, gbase, plane_bytes, mbarG);
+        if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
+        if (F > 1) bulk_prefetch_l2(gbase + (int64_t)npix, plane_bytes);
+    }
     if (tid < F) {
         const Box box = load_box(bp, c * F + tid);
         store_taps(sTaps + tid * kTapWords, taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
     }
-    if (STAGED) {
-        __syncthreads();                                   // barriers initialised before anyone waits
-        if (tid == 0) {
-            bulk_load(sG32, gbase, plane_bytes, mbarG);
-            if (F > 1) bulk_prefetch_l2(gbase + (int64_t)npix, plane_bytes);
-            if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
-        }
-    }
+    if (STAGED) __syncthreads();                           // barriers initialised before anyone waits
     if (!X_BY_COPY && NEED_PARAMS && XSMEM) {
         // (read by the first gather, which follows the barriers of the first build)
         const IO *xp = x + nc * (int64_t)npix;
