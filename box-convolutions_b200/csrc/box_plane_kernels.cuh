@@ -534,25 +534,25 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
 #pragma unroll
     for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
 
-    // The first copies are started by a thread of the second warp (when there is one), so that they do
-    // not queue behind the box arithmetic of the first warp's threads.
+    // The first copies are started as early as possible, by a thread of the second warp (when there is
+    // one) so that they do not queue behind the box arithmetic of the first warp's threads.  That thread
+    // initialises the barriers itself and so needs no CTA barrier before it uses them; the other
+    // threads first wait on them after the __syncthreads() below.
     const int starter = blockDim.x > 32 ? 32 : 0;
     if (STAGED && tid == starter) {
         mbar_init(mbarX, 1);
         mbar_init(mbarG, 1);
         fence_mbar_init();
+        grid_dependency_wait();      // grad_output and the input may come from the kernel in front
+        bulk_load(sG32, gbase, plane_bytes, mbarG);
+        if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
+        if (F > 1) bulk_prefetch_l2(gbase + (int64_t)npix, plane_bytes);
     }
     init_integral_padding(sI, g);
 
     // registers and shared memory only up to here; now global memory that the kernel in front of
     // this one in the stream may still be using
     grid_dependency_wait();
-    if (STAGED && tid == starter) {
-        // (the thread that initialised the barriers: it needs no barrier to use them)
-        bulk_load(sG32, gbase, plane_bytes, mbarG);
-        if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
-        if (F > 1) bulk_prefetch_l2(gbase + (int64_t)npix, plane_bytes);
-    }
     if (tid < F) {
         const Box box = load_box(bp, c * F + tid);
         store_taps(sTaps + tid * kTapWords, taps_mirrored(box.xmin, box.xmax, box.ymin, box.ymax, normalize, exact));
