@@ -403,12 +403,15 @@ forward_plane_kernel(const IO *__restrict__ x, BoxParams bp, IO *out, int C, int
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int cg = lane & 7, rg = lane >> 3;
 
+    // a hint only: the plane on its way to L2 while this CTA still waits for the kernel in front
+    if (FAST && IsFloat<IO>::value && threadIdx.x == 0 && part == 0)
+        bulk_prefetch_l2(x + nc * (int64_t)h * w, (uint32_t)(h * w) * 4u);
     Strip st[T];
 #pragma unroll
     for (int k = 0; k < T; ++k) st[k] = make_strip(g, sI32, warp + k * nwarps, cg, rg);
     init_integral_padding(sI, g);
 
-    // everything above touches registers and shared memory only; from here on the parameters and
+    // everything above touches registers and shared memory only (and hints); from here on the parameters and
     // the input are read, which the kernel in front of this one in the stream may have written
     grid_dependency_wait();
     if ((int)threadIdx.x < f_end - f_begin) {
@@ -543,6 +546,10 @@ backward_plane_kernel(const IO *__restrict__ x, const IO *__restrict__ grad_outp
         mbar_init(mbarX, 1);
         mbar_init(mbarG, 1);
         fence_mbar_init();
+        // While this CTA waits for the kernel in front of it, its first planes can already travel to L2
+        // (a hint: if that kernel is still writing them, L2 receives its writes as well).
+        bulk_prefetch_l2(gbase, plane_bytes);
+        if (NEED_PARAMS && X_BY_COPY) bulk_prefetch_l2(x + nc * (int64_t)npix, plane_bytes);
         grid_dependency_wait();      // grad_output and the input may come from the kernel in front
         bulk_load(sG32, gbase, plane_bytes, mbarG);
         if (NEED_PARAMS && X_BY_COPY) bulk_load(sX32, x + nc * (int64_t)npix, plane_bytes, mbarX);
